@@ -8,7 +8,8 @@ imparo-model/src/kv.rs:1353; groups by state kind, imparo-kv/src/state.rs:16-21)
 Every request also holds one state slot; each state entry has a float32 tensor
 [slots, *shape], zeroed when a request takes its slot (imparo-model/src/lib.rs:1951-1972).
 
-Arena layout per group: K and V each [entries, pages, page_size, kv_heads*head_dim].
+Arena layout per group: K [entries, pages, page_size, kv_heads*head_dim] and V the same with the value size
+(PagedKV.v_head_dim, the key size unless given).
 """
 from __future__ import annotations
 
@@ -98,9 +99,9 @@ class CacheManager:
         self.state: Dict[Tuple[int, int], torch.Tensor] = {}
         if device is not None:
             for g, key in enumerate(self.group_keys):
-                shape = (len(self.group_entries[g]), self.num_pages[g] + 1, self.page_size, key.width)
-                self.k_arena.append(torch.zeros(shape, dtype=kv_dtype, device=device))
-                self.v_arena.append(torch.zeros(shape, dtype=kv_dtype, device=device))
+                shape = (len(self.group_entries[g]), self.num_pages[g] + 1, self.page_size)
+                self.k_arena.append(torch.zeros(shape + (key.width,), dtype=kv_dtype, device=device))
+                self.v_arena.append(torch.zeros(shape + (key.v_width,), dtype=kv_dtype, device=device))
             # every fixed-size state tensor is a stretch of ONE flat float32 arena, [slots, *shape] each, so that
             # the slots of requests that start in a step are zeroed by one kernel of the step's own chain
             # (state_segments: per tensor its offset in the arena and its floats per slot)

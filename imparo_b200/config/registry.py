@@ -42,10 +42,10 @@ def _ensure_builtin() -> None:
 
 
 def resolve_architecture(values: dict) -> Architecture:
-    """Pick the architecture a config.json names: "architectures"[0], else "model_type".
+    """Pick the architecture a config.json names: "architectures"[0] (or "architecture"), else "model_type".
     Unknown name -> error listing the known ones (PlanError::UnknownArchitecture)."""
     _ensure_builtin()
-    names = values.get("architectures") or []
+    names = values.get("architectures") or values.get("architecture") or []
     if isinstance(names, str):
         names = [names]
     for n in names:

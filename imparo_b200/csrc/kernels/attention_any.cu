@@ -1,0 +1,205 @@
+// Attention over the paged cache for shapes and variants the specialised kernels do not take:
+// any head size up to 256 with a value size of its own, rotation of interleaved pairs (2i, 2i+1)
+// or of half-split pairs (i, i + n_rot/2) over the first n_rot dimensions with a magnitude on the
+// sines and cosines, an explicit score scale, a window, and a softmax whose denominator counts one
+// more term of score 0 that has no value ("sink": p_j = exp(s_j) / (1 + sum exp(s_j))).
+//
+//  (1) qkv_rotate_store: rows [q heads * hd | kv heads * hd | kv heads * vd] -> rotated queries,
+//      rotated keys and plain values written into their pages (K rows kv*hd wide, V rows kv*vd wide).
+//  (2) attention_any: one warp per (token, head); keys walked 32 at a time in position order, every
+//      lane scores one key; running max and sum in 32-bit; then the lanes accumulate the values, each
+//      owning dimensions lane, lane+32, ...  The walk depends only on (position, window).
+//      With a sink the running max starts at 0 and the running sum at 1: the extra term is a key
+//      of score 0 seen before all others.
+#include "common.cuh"
+
+namespace imparo {
+
+constexpr int ANY_MAX_HEAD = 256;
+constexpr int ANY_WARPS = 4;
+
+template <typename T>
+__global__ void __launch_bounds__(ANY_WARPS * 32)
+qkv_rotate_store_kernel(const T* __restrict__ qkv, const int* __restrict__ positions, const int* __restrict__ item_of_token,
+                        const float* __restrict__ inv_freq, int n_rot, int interleaved, float magnitude,
+                        T* __restrict__ q_out, T* __restrict__ k_cache, T* __restrict__ v_cache,
+                        const int* __restrict__ table, int max_blocks, int page_size, int n_pages,
+                        int nh, int nkv, int hd, int vd, int* status) {
+    pdl_trigger();
+    const int t = blockIdx.x;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int hh = blockIdx.y * ANY_WARPS + warp;
+    const int total = nh + 2 * nkv;
+    if (hh >= total) return;
+    const int pos = positions[t];
+    const bool is_q = hh < nh, is_k = !is_q && hh < nh + nkv;
+    const size_t in_width = (size_t)(nh + nkv) * hd + (size_t)nkv * vd;
+    const T* src;
+    T* dst = nullptr;
+    int bad_page = 0;
+    int n;                                                       // this head's size
+    if (is_q) {
+        src = qkv + (size_t)t * in_width + (size_t)hh * hd;
+        dst = q_out + ((size_t)t * nh + hh) * hd;
+        n = hd;
+    } else {
+        const int kvh = is_k ? hh - nh : hh - nh - nkv;
+        n = is_k ? hd : vd;
+        src = qkv + (size_t)t * in_width + (size_t)nh * hd + (is_k ? (size_t)kvh * hd : (size_t)nkv * hd + (size_t)kvh * vd);
+        const int blk = pos / page_size;
+        int page = -1;
+        if (blk < max_blocks) page = table[(size_t)item_of_token[t] * max_blocks + blk];
+        if (page < 0 || page >= n_pages) {
+            bad_page = page;
+        } else {
+            const size_t r = (size_t)page * page_size + (pos % page_size);
+            dst = is_k ? k_cache + r * ((size_t)nkv * hd) + (size_t)kvh * hd : v_cache + r * ((size_t)nkv * vd) + (size_t)kvh * vd;
+        }
+    }
+    pdl_wait();
+    if (dst == nullptr) {
+        if (lane == 0) report(status, IMPARO_ST_PAGE_RANGE, 41, t, bad_page);
+        return;
+    }
+    const int half = n_rot >> 1;
+    if ((is_q || is_k) && inv_freq && half > 0) {
+        for (int i = lane; i < half; i += 32) {
+            float sn, cs;
+            sincosf((float)pos * inv_freq[i], &sn, &cs);
+            sn *= magnitude; cs *= magnitude;
+            const int a = interleaved ? 2 * i : i, b = interleaved ? 2 * i + 1 : i + half;
+            const float u = to_f32(src[a]), v = to_f32(src[b]);
+            dst[a] = from_f32<T>(u * cs - v * sn);
+            dst[b] = from_f32<T>(v * cs + u * sn);
+        }
+        for (int d = n_rot + lane; d < n; d += 32) dst[d] = src[d];
+    } else {
+        for (int d = lane; d < n; d += 32) dst[d] = src[d];
+    }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(ANY_WARPS * 32)
+attention_any_kernel(const T* __restrict__ q, const T* __restrict__ k_cache, const T* __restrict__ v_cache,
+                     const int* __restrict__ positions, const int* __restrict__ item_of_token,
+                     const int* __restrict__ table, int max_blocks, int page_size, int n_pages,
+                     int window, float scale, int sink, T* __restrict__ out, int nh, int nkv, int hd, int vd, int* status) {
+    __shared__ float qbuf[ANY_WARPS][ANY_MAX_HEAD];
+    pdl_trigger();
+    pdl_wait();
+    const int t = blockIdx.x;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int h = blockIdx.y * ANY_WARPS + warp;
+    if (h >= nh) return;
+    const int kvh = h / (nh / nkv);
+    const int pos = positions[t];
+    const int* tab = table + (size_t)item_of_token[t] * max_blocks;
+    const size_t kw = (size_t)nkv * hd, vw = (size_t)nkv * vd;
+    float* qs = qbuf[warp];
+    const T* qrow = q + ((size_t)t * nh + h) * hd;
+    for (int d = lane; d < hd; d += 32) qs[d] = to_f32(qrow[d]);
+    __syncwarp();
+
+    const int lo = (window > 0 && pos + 1 > window) ? pos + 1 - window : 0;
+    constexpr int PER = ANY_MAX_HEAD / 32;
+    float acc[PER];
+#pragma unroll
+    for (int i = 0; i < PER; ++i) acc[i] = 0.f;
+    float m = sink ? 0.f : -INFINITY, l = sink ? 1.f : 0.f;
+
+    for (int base = lo; base <= pos; base += 32) {
+        const int j = base + lane;
+        float s = -INFINITY;
+        int rowi = -1;
+        if (j <= pos) {
+            const int blk = j / page_size;
+            const int page = blk < max_blocks ? tab[blk] : -1;
+            if (page < 0 || page >= n_pages) {
+                report(status, IMPARO_ST_PAGE_RANGE, 42, t, page);
+            } else {
+                rowi = page * page_size + (j % page_size);
+                const T* kp = k_cache + (size_t)rowi * kw + (size_t)kvh * hd;
+                float d = 0.f;
+                for (int c = 0; c < hd; ++c) d += to_f32(kp[c]) * qs[c];
+                s = d * scale;
+            }
+        }
+        const float m_new = fmaxf(m, warp_max(s));
+        if (m_new == -INFINITY) continue;
+        const float p = (rowi >= 0) ? expf(s - m_new) : 0.f;
+        const float corr = (m == -INFINITY) ? 0.f : expf(m - m_new);
+        l = l * corr + warp_sum(p);
+#pragma unroll
+        for (int i = 0; i < PER; ++i) acc[i] *= corr;
+        m = m_new;
+        const int cnt = min(32, pos - base + 1);
+        for (int jj = 0; jj < cnt; ++jj) {
+            const float pj = __shfl_sync(0xffffffffu, p, jj);
+            const int rj = __shfl_sync(0xffffffffu, rowi, jj);
+            if (rj < 0) continue;
+            const T* vp = v_cache + (size_t)rj * vw + (size_t)kvh * vd;
+#pragma unroll
+            for (int i = 0; i < PER; ++i) {
+                const int d = lane + 32 * i;
+                if (d < vd) acc[i] += pj * to_f32(vp[d]);
+            }
+        }
+    }
+    const float inv = l > 0.f ? 1.0f / l : 0.f;
+    T* orow = out + ((size_t)t * nh + h) * vd;
+#pragma unroll
+    for (int i = 0; i < PER; ++i) {
+        const int d = lane + 32 * i;
+        if (d < vd) orow[d] = from_f32<T>(acc[i] * inv);
+    }
+}
+
+}  // namespace imparo
+
+using namespace imparo;
+
+// qkv: [n_tok, nh*hd + nkv*hd + nkv*vd].  nkv == 0: queries only.
+extern "C" int imparo_qkv_rotate_store(const void* qkv, int dtype, const int* positions, const int* item_of_token,
+                                       const float* inv_freq, int n_rot, int interleaved, float magnitude,
+                                       void* q_out, void* k_cache, void* v_cache,
+                                       const int* table, int max_blocks, int page_size, int n_pages,
+                                       int n_tok, int nh, int nkv, int hd, int vd, int* status, cudaStream_t stream) {
+    if (n_tok <= 0) return 0;
+    if (hd < 1 || hd > ANY_MAX_HEAD || vd < 1 || vd > ANY_MAX_HEAD) return -3;
+    if (n_rot < 0 || n_rot > hd || (n_rot & 1)) return -4;
+    dim3 grid(n_tok, (nh + 2 * nkv + ANY_WARPS - 1) / ANY_WARPS);
+    if (dtype == IMPARO_DT_F32)
+        launch(qkv_rotate_store_kernel<float>, grid, dim3(ANY_WARPS * 32), 0, stream, (const float*)qkv, positions, item_of_token,
+               inv_freq, n_rot, interleaved, magnitude, (float*)q_out, (float*)k_cache, (float*)v_cache, table, max_blocks,
+               page_size, n_pages, nh, nkv, hd, vd, status);
+    else if (dtype == IMPARO_DT_BF16)
+        launch(qkv_rotate_store_kernel<__nv_bfloat16>, grid, dim3(ANY_WARPS * 32), 0, stream, (const __nv_bfloat16*)qkv, positions,
+               item_of_token, inv_freq, n_rot, interleaved, magnitude, (__nv_bfloat16*)q_out, (__nv_bfloat16*)k_cache,
+               (__nv_bfloat16*)v_cache, table, max_blocks, page_size, n_pages, nh, nkv, hd, vd, status);
+    else return -1;
+    IMPARO_CHECK_LAUNCH();
+    return 0;
+}
+
+extern "C" int imparo_attention_any(const void* q, const void* k_cache, const void* v_cache, int dtype,
+                                    const int* positions, const int* item_of_token,
+                                    const int* table, int max_blocks, int page_size, int n_pages,
+                                    int window, float scale, int sink, void* out,
+                                    int n_tok, int nh, int nkv, int hd, int vd, int* status, cudaStream_t stream) {
+    if (n_tok <= 0) return 0;
+    if (hd < 1 || hd > ANY_MAX_HEAD || vd < 1 || vd > ANY_MAX_HEAD) return -3;
+    if (nkv <= 0 || nh % nkv != 0) return -5;
+    dim3 grid(n_tok, (nh + ANY_WARPS - 1) / ANY_WARPS);
+    if (dtype == IMPARO_DT_F32)
+        launch(attention_any_kernel<float>, grid, dim3(ANY_WARPS * 32), 0, stream,
+               (const float*)q, (const float*)k_cache, (const float*)v_cache, positions, item_of_token, table,
+               max_blocks, page_size, n_pages, window, scale, sink, (float*)out, nh, nkv, hd, vd, status);
+    else if (dtype == IMPARO_DT_BF16)
+        launch(attention_any_kernel<__nv_bfloat16>, grid, dim3(ANY_WARPS * 32), 0, stream,
+               (const __nv_bfloat16*)q, (const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache, positions,
+               item_of_token, table, max_blocks, page_size, n_pages, window, scale, sink, (__nv_bfloat16*)out, nh, nkv, hd, vd,
+               status);
+    else return -1;
+    IMPARO_CHECK_LAUNCH();
+    return 0;
+}

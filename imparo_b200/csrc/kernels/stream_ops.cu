@@ -1,0 +1,198 @@
+// Row-wise kernels around the 32-bit residual stream that arrangements other than the plain
+// pre-norm block need: activations on their own, an RMS norm multiplied by a sigmoid gate, the
+// mean of several RMS-normed branches added into the stream with a factor, a scaled add, a
+// vector (and optionally the tokens' embedding rows) added to the stream, a soft cap on logits.
+//
+// All sums of squares are fixed trees over blockDim threads (common.cuh block_sum), so a row's
+// result never depends on which other rows are in the launch.  Norms, gates and the stream are
+// 32-bit in both precisions; only stored activations take the path's dtype.
+#include "common.cuh"
+
+namespace imparo {
+
+#define IMPARO_ACT_RELU2 0
+#define IMPARO_ACT_GELU_TANH 1
+#define IMPARO_ACT_SILU 2
+
+__device__ __forceinline__ float act_apply(float z, int kind) {
+    if (kind == IMPARO_ACT_RELU2) { const float r = fmaxf(z, 0.f); return r * r; }
+    if (kind == IMPARO_ACT_GELU_TANH) return 0.5f * z * (1.0f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
+    return silu(z);
+}
+
+// out[i] = act(x[i]); x and out may be the same buffer
+template <typename T>
+__global__ void act_rows_kernel(const T* x, T* out, size_t n, int kind) {
+    pdl_trigger();
+    pdl_wait();
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x)
+        out[i] = from_f32<T>(act_apply(to_f32(x[i]), kind));
+}
+
+// out[r, :] = o[r, :] / rms(o[r, :]) * w * sigmoid(gate[r, :]);  o is 32-bit, gate rows have their own stride
+template <typename T>
+__global__ void gated_rmsnorm_kernel(const float* __restrict__ o, const float* __restrict__ w, float eps,
+                                     const T* __restrict__ gate, size_t gate_stride, T* __restrict__ out, int width) {
+    __shared__ float scratch[33];
+    pdl_trigger();
+    pdl_wait();
+    const int r = blockIdx.x;
+    const float* orow = o + (size_t)r * width;
+    const T* g = gate + (size_t)r * gate_stride;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < width; i += blockDim.x) { const float v = orow[i]; ss += v * v; }
+    ss = block_sum(ss, scratch);
+    const float scale = 1.0f / sqrtf(ss / (float)width + eps);
+    for (int i = threadIdx.x; i < width; i += blockDim.x) {
+        const float gv = to_f32(g[i]);
+        out[(size_t)r * width + i] = from_f32<T>(orow[i] * scale * w[i] * (1.0f / (1.0f + expf(-gv))));
+    }
+}
+
+// x[r, :] += coef * sum_b rms(branch_b[r, :]) * w_b  +  extra_coef * extra[r, :]
+struct Branches {
+    const float* b[4];
+    const float* w[4];
+};
+
+__global__ void norm_mean_add_kernel(float* __restrict__ x, Branches br, int n_branches, float eps, float coef,
+                                     const float* __restrict__ extra, float extra_coef, int width) {
+    __shared__ float scratch[33];
+    pdl_trigger();
+    pdl_wait();
+    const int r = blockIdx.x;
+    float scale[4];
+    for (int b = 0; b < n_branches; ++b) {
+        const float* row = br.b[b] + (size_t)r * width;
+        float ss = 0.f;
+        for (int i = threadIdx.x; i < width; i += blockDim.x) { const float v = row[i]; ss += v * v; }
+        ss = block_sum(ss, scratch);
+        scale[b] = 1.0f / sqrtf(ss / (float)width + eps);
+    }
+    float* xr = x + (size_t)r * width;
+    for (int i = threadIdx.x; i < width; i += blockDim.x) {
+        float s = 0.f;
+        for (int b = 0; b < n_branches; ++b) s += br.b[b][(size_t)r * width + i] * scale[b] * br.w[b][i];
+        float v = coef * s;
+        if (extra) v += extra_coef * extra[(size_t)r * width + i];
+        xr[i] += v;
+    }
+}
+
+__global__ void add_scaled_kernel(float* __restrict__ x, const float* __restrict__ y, float coef, size_t n) {
+    pdl_trigger();
+    pdl_wait();
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x)
+        x[i] += coef * y[i];
+}
+
+// x[t, :] += (table[ids[t], :] if table) + (vec[:] if vec)
+template <typename T>
+__global__ void stream_inject_kernel(float* __restrict__ x, const T* __restrict__ table, const int* __restrict__ ids,
+                                     const float* __restrict__ vec, int width, int vocab, int* status) {
+    pdl_trigger();
+    pdl_wait();
+    const int t = blockIdx.x;
+    const T* row = nullptr;
+    if (table) {
+        int id = ids[t];
+        if (id < 0 || id >= vocab) {
+            if (threadIdx.x == 0) report(status, IMPARO_ST_TOKEN_RANGE, 40, t, id);
+            id = 0;
+        }
+        row = table + (size_t)id * width;
+    }
+    float* xr = x + (size_t)t * width;
+    for (int i = threadIdx.x; i < width; i += blockDim.x) {
+        float v = xr[i];
+        if (row) v += to_f32(row[i]);
+        if (vec) v += vec[i];
+        xr[i] = v;
+    }
+}
+
+__global__ void softcap_kernel(float* __restrict__ x, size_t n, float cap) {
+    pdl_trigger();
+    pdl_wait();
+    const float inv = 1.0f / cap;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x)
+        x[i] = cap * tanhf(x[i] * inv);
+}
+
+}  // namespace imparo
+
+using namespace imparo;
+
+static inline unsigned flat_grid(size_t n) {
+    const size_t b = (n + 255) / 256;
+    return (unsigned)(b < 1 ? 1 : (b > 65535 ? 65535 : b));
+}
+
+extern "C" int imparo_act_rows(const void* x, void* out, int dtype, long long n, int kind, cudaStream_t stream) {
+    if (n <= 0) return 0;
+    if (kind < 0 || kind > 2) return -22;
+    if (dtype == IMPARO_DT_F32)
+        launch(act_rows_kernel<float>, dim3(flat_grid(n)), dim3(256), 0, stream, (const float*)x, (float*)out, (size_t)n, kind);
+    else if (dtype == IMPARO_DT_BF16)
+        launch(act_rows_kernel<__nv_bfloat16>, dim3(flat_grid(n)), dim3(256), 0, stream, (const __nv_bfloat16*)x,
+               (__nv_bfloat16*)out, (size_t)n, kind);
+    else return -1;
+    IMPARO_CHECK_LAUNCH();
+    return 0;
+}
+
+extern "C" int imparo_gated_rmsnorm(const float* o, const float* w, float eps, const void* gate, long long gate_stride,
+                                    void* out, int dtype, int n_rows, int width, cudaStream_t stream) {
+    if (n_rows <= 0) return 0;
+    const int threads = width >= 1024 ? 256 : 128;
+    if (dtype == IMPARO_DT_F32)
+        launch(gated_rmsnorm_kernel<float>, dim3(n_rows), dim3(threads), 0, stream, o, w, eps, (const float*)gate,
+               (size_t)gate_stride, (float*)out, width);
+    else if (dtype == IMPARO_DT_BF16)
+        launch(gated_rmsnorm_kernel<__nv_bfloat16>, dim3(n_rows), dim3(threads), 0, stream, o, w, eps,
+               (const __nv_bfloat16*)gate, (size_t)gate_stride, (__nv_bfloat16*)out, width);
+    else return -1;
+    IMPARO_CHECK_LAUNCH();
+    return 0;
+}
+
+extern "C" int imparo_norm_mean_add(float* x, int n_branches, const float* const* branches, const float* const* weights,
+                                    float eps, float coef, const float* extra, float extra_coef, int n_rows, int width,
+                                    cudaStream_t stream) {
+    if (n_rows <= 0) return 0;
+    if (n_branches < 0 || n_branches > 4) return -2;
+    Branches br = {};
+    for (int b = 0; b < n_branches; ++b) { br.b[b] = branches[b]; br.w[b] = weights[b]; }
+    launch(norm_mean_add_kernel, dim3(n_rows), dim3(width >= 1024 ? 256 : 128), 0, stream, x, br, n_branches, eps, coef, extra,
+           extra_coef, width);
+    IMPARO_CHECK_LAUNCH();
+    return 0;
+}
+
+extern "C" int imparo_add_scaled(float* x, const float* y, float coef, long long n, cudaStream_t stream) {
+    if (n <= 0) return 0;
+    launch(add_scaled_kernel, dim3(flat_grid(n)), dim3(256), 0, stream, x, y, coef, (size_t)n);
+    IMPARO_CHECK_LAUNCH();
+    return 0;
+}
+
+extern "C" int imparo_stream_inject(float* x, const void* table, int dtype, const int* ids, const float* vec, int n_tok,
+                                    int width, int vocab, int* status, cudaStream_t stream) {
+    if (n_tok <= 0 || (!table && !vec)) return 0;
+    if (dtype == IMPARO_DT_F32)
+        launch(stream_inject_kernel<float>, dim3(n_tok), dim3(128), 0, stream, x, (const float*)table, ids, vec, width, vocab, status);
+    else if (dtype == IMPARO_DT_BF16)
+        launch(stream_inject_kernel<__nv_bfloat16>, dim3(n_tok), dim3(128), 0, stream, x, (const __nv_bfloat16*)table, ids, vec,
+               width, vocab, status);
+    else return -1;
+    IMPARO_CHECK_LAUNCH();
+    return 0;
+}
+
+extern "C" int imparo_softcap(float* x, long long n, float cap, cudaStream_t stream) {
+    if (n <= 0) return 0;
+    if (!(cap > 0.f)) return -2;
+    launch(softcap_kernel, dim3(flat_grid(n)), dim3(256), 0, stream, x, (size_t)n, cap);
+    IMPARO_CHECK_LAUNCH();
+    return 0;
+}

@@ -105,6 +105,15 @@ def _declare_kernels(lib):
     _declare(lib, "imparo_take_sampled_tokens", [P, P, P, I, I, S])
     _declare(lib, "imparo_selftest_wait_limit", [P, I, P, S])
     _declare(lib, "imparo_zero_state_slots", [P, P, I, c_int64, P, I, I, P, S])
+    _declare(lib, "imparo_act_rows", [P, P, I, c_int64, I, S])
+    _declare(lib, "imparo_gated_rmsnorm", [P, P, c_float, P, c_int64, P, I, I, I, S])
+    _declare(lib, "imparo_norm_mean_add", [P, I, P, P, c_float, c_float, P, c_float, I, I, S])
+    _declare(lib, "imparo_add_scaled", [P, P, c_float, c_int64, S])
+    _declare(lib, "imparo_stream_inject", [P, P, I, P, P, I, I, I, P, S])
+    _declare(lib, "imparo_softcap", [P, c_int64, c_float, S])
+    _declare(lib, "imparo_qkv_rotate_store", [P, I, P, P, P, I, I, c_float, P, P, P, P, I, I, I, I, I, I, I, I, P, S])
+    _declare(lib, "imparo_attention_any", [P, P, P, I, P, P, P, I, I, I, I, c_float, I, P, I, I, I, I, I, P, S])
+    _declare(lib, "imparo_linear_attention_recurrent", [P, P, P, c_int64, I, I, P, P, P, P, I, I, P, I, I, I, P, S])
 
 
 def _declare_host(lib):

@@ -925,3 +925,144 @@ def sample_rows(logits, temperature, uniform, out) -> None:
             return
     _check(_lib.kernels().imparo_sample_rows(_ptr(logits), _ptr(temperature), _ptr(uniform), _ptr(out), n, vocab,
                                              logits.stride(0), _stream()), "sample_rows")
+
+
+# ---- stream operations of arrangements other than the pre-norm block (csrc/kernels/stream_ops.cu) ----------
+ACTIVATIONS = {"relu2": 0, "gelu_tanh": 1, "silu": 2}
+
+
+def activation(x: torch.Tensor, out: torch.Tensor, kind: str) -> None:
+    """out = act(x) elementwise (relu2: relu(x)^2, gelu_tanh, silu); out may be x."""
+    _cuda(x, out)
+    _need(kind in ACTIVATIONS, f"activation: unknown kind '{kind}' (known: {', '.join(sorted(ACTIVATIONS))})")
+    _need(x.shape == out.shape and x.dtype == out.dtype, "activation: out must match x")
+    _check(_lib.kernels().imparo_act_rows(_ptr(x), _ptr(out), _code(x), x.numel(), ACTIVATIONS[kind], _stream()), "activation")
+
+
+def gated_rmsnorm(o: torch.Tensor, w: torch.Tensor, eps: float, gate: torch.Tensor, out: torch.Tensor) -> None:
+    """out[r] = o[r] / rms(o[r]) * w * sigmoid(gate[r]).  o: float32 [rows, width]; gate: [rows, width] of out's
+    dtype, rows may be strided (a stretch of a wider product)."""
+    _need(o.is_cuda and gate.is_cuda and out.is_cuda and w.is_cuda, "kernels run on CUDA tensors only (there is no CPU path)")
+    n, width = out.shape
+    _need(o.dtype == torch.float32 and o.shape == (n, width) and o.is_contiguous() and out.is_contiguous(), "gated_rmsnorm: o float32 [rows, width]")
+    _need(w.dtype == torch.float32 and w.numel() == width, "gated_rmsnorm: weight float32 [width]")
+    _need(gate.shape == (n, width) and gate.dtype == out.dtype and gate.stride(1) == 1, "gated_rmsnorm: gate [rows, width] of the output dtype")
+    _check(_lib.kernels().imparo_gated_rmsnorm(_ptr(o), _ptr(w), float(eps), _ptr(gate), gate.stride(0), _ptr(out), _code(out),
+                                               n, width, _stream()), "gated_rmsnorm")
+
+
+def norm_mean_add(x: torch.Tensor, branches, weights, eps: float, coef: float, extra: Optional[torch.Tensor] = None,
+                  extra_coef: float = 0.0) -> None:
+    """x += coef * sum_b rms(branches[b]) * weights[b] + extra_coef * extra, row by row; all float32 [rows, width],
+    up to four branches."""
+    import ctypes
+    settle(x)
+    _cuda(x, extra, *branches, *weights)
+    n, width = x.shape
+    _need(1 <= len(branches) <= 4 and len(weights) == len(branches), "norm_mean_add: one to four branches, a weight each")
+    for b, w in zip(branches, weights):
+        _need(b.dtype == torch.float32 and b.shape == (n, width) and w.dtype == torch.float32 and w.numel() == width,
+              "norm_mean_add: branches float32 [rows, width], weights float32 [width]")
+    _need(x.dtype == torch.float32 and (extra is None or (extra.dtype == torch.float32 and extra.shape == (n, width))),
+          "norm_mean_add: stream and extra are float32 [rows, width]")
+    bp = (ctypes.c_void_p * 4)(*[b.data_ptr() for b in branches])
+    wp = (ctypes.c_void_p * 4)(*[w.data_ptr() for w in weights])
+    _check(_lib.kernels().imparo_norm_mean_add(_ptr(x), len(branches), bp, wp, float(eps), float(coef), _ptr(extra),
+                                               float(extra_coef), n, width, _stream()), "norm_mean_add")
+
+
+def add_scaled(x: torch.Tensor, y: torch.Tensor, coef: float) -> None:
+    """x += coef * y (float32, same shape)."""
+    settle(x)
+    _cuda(x, y)
+    _need(x.dtype == torch.float32 and y.dtype == torch.float32 and x.shape == y.shape, "add_scaled: float32 tensors of one shape")
+    _check(_lib.kernels().imparo_add_scaled(_ptr(x), _ptr(y), float(coef), x.numel(), _stream()), "add_scaled")
+
+
+def stream_inject(x: torch.Tensor, table: Optional[torch.Tensor], ids: Optional[torch.Tensor], vec: Optional[torch.Tensor],
+                  status: torch.Tensor) -> None:
+    """x[t] += table[ids[t]] (when table is given) + vec (when given).  x: float32 [tokens, width]."""
+    settle(x)
+    _cuda(x, table, ids, vec, status)
+    n, width = x.shape
+    _need(x.dtype == torch.float32, "stream_inject: the stream is float32")
+    if table is not None:
+        _need(table.shape[1] == width and ids is not None and ids.dtype == torch.int32 and ids.numel() >= n,
+              "stream_inject: table [vocab, width], int32 ids per row")
+    _need(vec is None or (vec.dtype == torch.float32 and vec.numel() == width), "stream_inject: vec float32 [width]")
+    _check(_lib.kernels().imparo_stream_inject(_ptr(x), _ptr(table), _code(table) if table is not None else F32, _ptr(ids),
+                                               _ptr(vec), n, width, table.shape[0] if table is not None else 0, _ptr(status),
+                                               _stream()), "stream_inject")
+
+
+def softcap(x: torch.Tensor, cap: float) -> None:
+    """x = cap * tanh(x / cap) in place (float32)."""
+    _cuda(x)
+    _need(x.dtype == torch.float32, "softcap: float32 logits")
+    _check(_lib.kernels().imparo_softcap(_ptr(x), x.numel(), float(cap), _stream()), "softcap")
+
+
+# ---- attention of any shape and variant (csrc/kernels/attention_any.cu) ------------------------------------
+def qkv_rotate_store(qkv, positions, item_of_token, inv_freq, n_rot, interleaved, magnitude, q_out, k_cache, v_cache,
+                     table, page_size, n_pages, nh, nkv, hd, vd, status) -> None:
+    """qkv [T, nh*hd + nkv*hd + nkv*vd] -> q_out [T, nh*hd] rotated; k rotated and v written into their pages
+    (K rows nkv*hd wide, V rows nkv*vd wide).  Rotation over the first n_rot dims: pairs (2i, 2i+1) when interleaved,
+    else (i, i + n_rot/2); sines and cosines times magnitude.  nkv == 0: queries only."""
+    _cuda(qkv, positions, item_of_token, inv_freq, q_out, k_cache, v_cache, table, status)
+    T = q_out.shape[0]
+    _need(tuple(qkv.shape) == (T, nh * hd + nkv * (hd + vd)) and q_out.shape[1] == nh * hd and qkv.dtype == q_out.dtype,
+          "qkv_rotate_store: widths")
+    _need(positions.dtype == torch.int32 and item_of_token.dtype == torch.int32 and positions.numel() >= T
+          and item_of_token.numel() >= T, "positions / item_of_token must be int32 per token")
+    if nkv:
+        _need(k_cache.dtype == qkv.dtype and v_cache.dtype == qkv.dtype, "cache dtype must match activations")
+        _need(k_cache.numel() >= n_pages * page_size * nkv * hd and v_cache.numel() >= n_pages * page_size * nkv * vd,
+              "cache arena smaller than n_pages")
+        _need(table.dtype == torch.int32 and table.dim() == 2, "block table must be int32 [items, blocks]")
+    if inv_freq is not None:
+        _need(inv_freq.dtype == torch.float32 and inv_freq.numel() >= n_rot // 2, "inv_freq must be float32 [n_rot/2]")
+    _check(_lib.kernels().imparo_qkv_rotate_store(
+        _ptr(qkv), _code(q_out), _ptr(positions), _ptr(item_of_token), _ptr(inv_freq), int(n_rot), int(bool(interleaved)),
+        float(magnitude), _ptr(q_out), _ptr(k_cache), _ptr(v_cache), _ptr(table), table.shape[1] if table is not None else 0,
+        page_size, n_pages, T, nh, nkv, hd, vd, _ptr(status), _stream()), "qkv_rotate_store")
+
+
+def attention_any(q, k_cache, v_cache, positions, item_of_token, table, page_size, n_pages, window, scale, sink,
+                  out, nh, nkv, hd, vd, status) -> None:
+    """General attention: any head size hd and value size vd up to 256, optional window, optional sink (one more
+    term of score 0 and no value in the softmax's denominator).  out [T, nh*vd]."""
+    _cuda(q, k_cache, v_cache, positions, item_of_token, table, out, status)
+    T = q.shape[0]
+    _need(q.shape == (T, nh * hd) and out.shape == (T, nh * vd) and out.dtype == q.dtype, "attention_any: q/out shapes")
+    _need(k_cache.dtype == q.dtype and v_cache.dtype == q.dtype, "cache dtype must match q")
+    _need(k_cache.numel() >= n_pages * page_size * nkv * hd and v_cache.numel() >= n_pages * page_size * nkv * vd,
+          "cache arena smaller than n_pages")
+    _need(table.dtype == torch.int32 and table.dim() == 2, "block table must be int32 [items, blocks]")
+    _check(_lib.kernels().imparo_attention_any(
+        _ptr(q), _ptr(k_cache), _ptr(v_cache), _code(q), _ptr(positions), _ptr(item_of_token), _ptr(table),
+        table.shape[1], page_size, n_pages, int(window or 0), float(scale), int(bool(sink)), _ptr(out), T, nh, nkv, hd, vd,
+        _ptr(status), _stream()), "attention_any")
+
+
+# ---- linear attention with decay (csrc/kernels/linear_attention.cu) -------------------------------------------
+def linear_attention(qkv: torch.Tensor, q_off: int, k_off: int, v_off: int, decay: torch.Tensor, state: torch.Tensor,
+                     item_row_start, item_slot, n_items: int, out: torch.Tensor, heads: int, dim: int, vdim: int,
+                     status: torch.Tensor, act: Optional[str] = "silu") -> None:
+    """Per request and head: S = decay * S + k v^T, o = S^T q over the request's rows in order, from and into
+    state[slot].  qkv: [T, width] rows holding q (heads*dim) at column q_off, k at k_off, v (heads*vdim) at v_off;
+    act: "silu" or None, applied to q, k and v.  state: float32 [slots, heads, dim, vdim]; out: float32 [T, heads*vdim]."""
+    _need(qkv.is_cuda and qkv.stride(1) == 1, "kernels run on CUDA tensors only (there is no CPU path)")
+    _cuda(decay, state, item_row_start, item_slot, out, status)
+    T = qkv.shape[0]
+    _need(act in ("silu", None), "linear_attention: act is 'silu' or None")
+    _need(decay.dtype == torch.float32 and decay.numel() == heads, "linear_attention: decay float32 [heads]")
+    _need(state.dtype == torch.float32 and tuple(state.shape[1:]) == (heads, dim, vdim), "linear_attention: state float32 [slots, heads, dim, vdim]")
+    _need(out.dtype == torch.float32 and out.shape == (T, heads * vdim), "linear_attention: out float32 [tokens, heads*vdim]")
+    _need(max(q_off, k_off) + heads * dim <= qkv.shape[1] and v_off + heads * vdim <= qkv.shape[1], "linear_attention: offsets")
+    _need(item_row_start.numel() >= n_items + 1 and item_slot.numel() >= n_items, "linear_attention: item arrays")
+    es = qkv.element_size()
+    base = qkv.data_ptr()
+    _check(_lib.kernels().imparo_linear_attention_recurrent(
+        base + q_off * es, base + k_off * es, base + v_off * es, qkv.stride(0), _code(qkv), int(act == "silu"), _ptr(decay),
+        _ptr(state), _ptr(item_row_start), _ptr(item_slot), int(n_items), state.shape[0], _ptr(out), heads, dim, vdim,
+        _ptr(status), _stream()), "linear_attention")

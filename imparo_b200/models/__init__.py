@@ -1,2 +1,3 @@
 """Built-in architectures; importing this package registers them."""
 from . import lfm2  # noqa: F401
+from . import vipotar  # noqa: F401

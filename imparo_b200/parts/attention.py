@@ -21,7 +21,16 @@ class AttentionMixer(Part):
     """params: hidden, n_heads, n_kv_heads, head_dim, eps, window (None or int), position
     (PartSpec), qk_norm (bool, default True: per-head RMS norm of q and k with a weight each; False: none, and
     no norm tensors are declared), bias (bool, default False: True declares optional q/k/v/out biases, used
-    when the file carries them), names (optional dict of tensor names)."""
+    when the file carries them), names (optional dict of tensor names), v_head_dim (the value size per head, default
+    head_dim), scale (the factor on q.k, default 1/sqrt(head_dim)), sink (bool, default False: the softmax's denominator
+    counts one more term of score 0 that has no value, p_j = exp(s_j) / (1 + sum exp(s_j))).
+
+    Shapes and variants the specialised kernels do not take (a value size of its own, a sink, a rotation of interleaved
+    pairs or with a magnitude, a head size that is no multiple of 16) run on the general pair of kernels
+    (ops.qkv_rotate_store, ops.attention_any).
+
+    forward(..., accumulate=False) overwrites `residual` (then any float32 [tokens, hidden] buffer) instead of adding
+    into it: a mixer that runs beside others hands its output to whoever combines them."""
     adds_with_linear = True
 
 
@@ -37,24 +46,32 @@ class AttentionMixer(Part):
         self.nh = int(p["n_heads"])
         self.nkv = int(p["n_kv_heads"])
         self.hd = int(p["head_dim"])
-        self.eps = float(p["eps"])
+        self.vd = int(p.get("v_head_dim") or self.hd)
+        self.sink = bool(p.get("sink", False))
+        self.eps = float(p.get("eps", 0.0))
         self.window = int(p["window"]) if p.get("window") else None
         self.qk_norm = bool(p.get("qk_norm", True))
         self.bias = bool(p.get("bias", False))
         if self.nh % self.nkv:
             raise ValueError(f"attention: kv heads {self.nkv} must divide heads {self.nh}")
-        if self.hd % 16 or not 16 <= self.hd <= 256:
-            raise ValueError(f"attention: head size {self.hd} is not supported by the kernels "
-                             "(multiples of 16 from 16 to 256)")
-        self.scale = 1.0 / math.sqrt(self.hd)
+        if not 1 <= self.hd <= 256 or not 1 <= self.vd <= 256:
+            raise ValueError(f"attention: head size {self.hd} / value size {self.vd} is not supported by the kernels (1 to 256)")
+        self.scale = float(p["scale"]) if p.get("scale") is not None else 1.0 / math.sqrt(self.hd)
         self.names = {k: prefix + v for k, v in {**self.NAMES, **p.get("names", {})}.items()}
         self.position = make_part("position", p.get("position", PartSpec("none")), prefix, rt)
+        # the general kernels take what the specialised ones (per-head norm + half-split rotation, equal sizes,
+        # plain softmax) do not
+        self.general = (self.sink or self.vd != self.hd or self.hd % 16 != 0 or self.position.interleaved
+                        or self.position.magnitude != 1.0)
+        if self.general and (self.qk_norm or self.bias):
+            raise ValueError("attention: per-head q/k norms and biases are not available together with a sink, a value size "
+                             "of its own, an interleaved or scaled rotation, or a head size that is no multiple of 16")
         self.w_qkv = self.w_o = self.q_norm = self.k_norm = self.b_qkv = self.b_o = None
 
     def weight_specs(self):
-        n, H, hd = self.names, self.hidden, self.hd
+        n, H, hd, vd = self.names, self.hidden, self.hd, self.vd
         specs = [WeightSpec(n["q"], ((self.nh * hd, H),)), WeightSpec(n["k"], ((self.nkv * hd, H),)),
-                 WeightSpec(n["v"], ((self.nkv * hd, H),)), WeightSpec(n["o"], ((H, self.nh * hd),))]
+                 WeightSpec(n["v"], ((self.nkv * vd, H),)), WeightSpec(n["o"], ((H, self.nh * vd),))]
         if self.qk_norm:
             specs += [WeightSpec(n["q_norm"], ((hd,),), role="vector", init=("norm",)),
                       WeightSpec(n["k_norm"], ((hd,),), role="vector", init=("norm",))]
@@ -83,7 +100,7 @@ class AttentionMixer(Part):
         self.position.bind(tensors)
 
     def cache_specs(self):
-        return (PagedKV(self.nkv, self.hd, self.window),)
+        return (PagedKV(self.nkv, self.hd, self.window, None if self.vd == self.hd else self.vd),)
 
     def _partials_room(self, upper_context: int) -> int:
         """Partial results (per head) that the split-key attention of this engine's largest step of one-token rows
@@ -97,8 +114,31 @@ class AttentionMixer(Part):
         context = max(int(upper_context), min(most.get("context", 0), 1 << 17))
         return (8 * ops.sm_count() + rows * self.nkv * (1 + -(-context // 512))) * (self.nh // self.nkv)
 
-    def forward(self, x, batch, caches, residual):
+    def _forward_general(self, x, batch, kv, residual, accumulate):
+        """Unfused: product, rotation + cache write, attention (one warp per token and head), output product."""
+        rt, T = self.rt, x.shape[0]
+        nh, hd, vd = self.nh, self.hd, self.vd
+        nkv = self.nkv if kv.writes else 0
+        width = nh * hd + nkv * (hd + vd)
+        qkv = rt.workspace.get("attn_qkv", (T, width), rt.act_dtype, first="tokens")
+        ops.linear(x, self.w_qkv[:width], qkv, status=rt.status)
+        q = rt.workspace.get("attn_q", (T, nh * hd), rt.act_dtype, first="tokens")
+        rot = self.position.rotary()
+        inv_freq, n_rot = rot if rot is not None else (None, 0)
+        table = batch.tables[kv.group]
+        ops.qkv_rotate_store(qkv, batch.positions, batch.item_of_token, inv_freq, n_rot, self.position.interleaved,
+                             self.position.magnitude, q, kv.k, kv.v, table, kv.page_size, kv.n_pages, nh, nkv, hd, vd, rt.status)
+        out = rt.workspace.get("attn_out", (T, nh * vd), rt.act_dtype, first="tokens")
+        ops.attention_any(q, kv.k, kv.v, batch.positions, batch.item_of_token, table, kv.page_size, kv.n_pages, self.window,
+                          self.scale, self.sink, out, nh, self.nkv, hd, vd, rt.status)
+        ops.linear(out, self.w_o, residual, accumulate=accumulate, status=rt.status)
+
+    def forward(self, x, batch, caches, residual, accumulate=True):
         kv = caches[0]
+        if self.general:
+            return self._forward_general(x, batch, kv, residual, accumulate)
+        if not accumulate:
+            residual.zero_()              # the specialised path's products add; the caller's buffer starts from nothing
         rt, T = self.rt, x.shape[0]
         nh, hd = self.nh, self.hd
         nkv = self.nkv if kv.writes else 0          # a reader of another entry's cache computes q only

@@ -9,6 +9,7 @@ model it is in.  Kinds:
   "position"     tables / apply for queries and keys
   "block"        forward(x, batch, caches, only_rows) arranges norm, mixer, feed-forward
   "embedding"    forward(batch)                       -> the 32-bit residual stream [tokens, width]
+  "stream_op"    forward(x, batch)                    changes the 32-bit stream in place before a schedule entry
   "head"         forward(h)                           -> 32-bit logits
 
 x is the normed input in the activation dtype (bfloat16, or float32 in the 32-bit

@@ -99,3 +99,67 @@ class PreNormResidualBlock(Block):
         else:
             ops.settle(x)
             call()
+
+
+class ParallelResidualBlock(Block):
+    """One norm, both sublayers read its output, one add:  h = norm(x);  x += s * (mixer(h) + feed_forward(h)).
+
+    params: layer (LayerSpec).  The layer's mixer_norm is the one norm; feed_forward may be None (the layer has none);
+    layer.params["residual_scale"] is s (default 1).  A mixer or feed-forward that is to be scaled declares
+    takes_scale (its forward has a `scale` keyword).  When the mixer can take the other sublayer's output along
+    (forward(..., extra=, extra_scale=), as the side-by-side mixer does) and the feed-forward can write into a
+    buffer (forward_into), the feed-forward runs first and both are added in the mixer's one pass over the stream."""
+
+    def __init__(self, params, prefix, rt):
+        super().__init__(params, prefix, rt)
+        spec = params["layer"]
+        self.scale = float(spec.params.get("residual_scale", 1.0))
+        self.norm = make_part("norm", spec.mixer_norm, prefix, rt)
+        self.mixer = make_part("mixer", spec.mixer, prefix, rt)
+        self.ff = make_part("feed_forward", spec.feed_forward, prefix, rt) if spec.feed_forward is not None else None
+        self.parts = tuple(p for p in (self.norm, self.mixer, self.ff) if p is not None)
+        for p in self.parts[1:]:
+            if self.scale != 1.0 and not getattr(p, "takes_scale", False):
+                raise ValueError(f"parallel block: {type(p).__name__} cannot scale its output (residual_scale {self.scale})")
+        self.graph_safe = all(p.graph_safe for p in self.parts)
+        self.picks_rows = False
+        import inspect
+        self._one_pass = (self.ff is not None and hasattr(self.ff, "forward_into")
+                          and "extra" in inspect.signature(self.mixer.forward).parameters)
+
+    def weight_specs(self):
+        return [w for p in self.parts for w in p.weight_specs()]
+
+    def bind(self, tensors):
+        for p in self.parts:
+            p.bind(tensors)
+
+    def cache_specs(self):
+        return self.mixer.cache_specs()
+
+    def forward(self, x, batch, caches, only_rows=None):
+        from ..kernels import ops
+        import torch
+        probe = self.rt.probe if self.rt.probe_now else None
+        ops.settle(x)
+        if probe:
+            probe("stream_in", x)
+        h = self.norm.forward(x, tag="normed_mixer")
+        if probe:
+            probe("mixer_norm", h)
+        kw = {"scale": self.scale} if self.scale != 1.0 else {}
+        if self._one_pass and not probe:
+            y = self.rt.workspace.get("ffn_out", (x.shape[0], x.shape[1]), torch.float32, first="tokens")
+            self.ff.forward_into(h, y)
+            self.mixer.forward(h, batch, caches, x, extra=y, extra_scale=self.scale, **kw)
+        else:
+            self.mixer.forward(h, batch, caches, x, **kw)
+            ops.settle(x)
+            if probe:
+                probe("stream_mixer", x)
+            if self.ff is not None:
+                self.ff.forward(h, batch, x, **kw)
+        ops.settle(x)
+        if probe:
+            probe("stream_out", x)
+        return None

@@ -38,13 +38,15 @@ class TokenEmbedding(Part):
 
 
 class LinearHead(Part):
-    """params: vocab, width, name (the table's own tensor, or the embedding's when tied)."""
+    """params: vocab, width, name (the table's own tensor, or the embedding's when tied), softcap (optional c > 0:
+    logits become c * tanh(logits / c))."""
 
     def __init__(self, params, prefix, rt):
         super().__init__(params, prefix, rt)
         self.vocab = int(params["vocab"])
         self.width = int(params["width"])
         self.name = prefix + params["name"]
+        self.softcap = float(params["softcap"]) if params.get("softcap") else None
         self.table = None
 
     def weight_specs(self):
@@ -56,4 +58,6 @@ class LinearHead(Part):
     def forward(self, h: torch.Tensor) -> torch.Tensor:
         logits = self.rt.workspace.get("logits", (h.shape[0], self.vocab), torch.float32, first="rows")
         ops.linear(h, self.table, logits, status=self.rt.status)
+        if self.softcap is not None:
+            ops.softcap(logits, self.softcap)
         return logits

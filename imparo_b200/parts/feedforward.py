@@ -40,3 +40,51 @@ class SwiGLU(Part):
         # [T, 2F] is made only where no kernel has silu(gate) * up in its epilogue
         ops.linear_swiglu(x, self.w_gu, h, rt.status, tmp=lambda: rt.workspace.get("ffn_gu", (T, 2 * F), rt.act_dtype, first="tokens"))
         ops.linear(h, self.w_down, residual, accumulate=True, status=rt.status)
+
+
+class DenseFeedForward(Part):
+    """down(act(up(x))) with one activation on its own: params hidden, ff, act ("relu2": relu(z)^2, "gelu_tanh",
+    "silu"), names (optional).
+
+    forward(x, batch, residual, scale=1.0) adds scale * output into the stream; forward_into(x, out) writes the
+    output into a float32 buffer instead (for an arrangement that adds several sublayers in one pass)."""
+    takes_scale = True
+
+    NAMES = {"up": "up", "down": "down"}
+
+    def __init__(self, params, prefix, rt):
+        super().__init__(params, prefix, rt)
+        self.hidden = int(params["hidden"])
+        self.ff = int(params["ff"])
+        self.act = params.get("act", "relu2")
+        if self.act not in ops.ACTIVATIONS:
+            raise ValueError(f"feed-forward: unknown activation '{self.act}'; known: {', '.join(sorted(ops.ACTIVATIONS))}")
+        self.names = {k: prefix + v for k, v in {**self.NAMES, **params.get("names", {})}.items()}
+        self.w_up = self.w_down = None
+
+    def weight_specs(self):
+        n, H, F = self.names, self.hidden, self.ff
+        return [WeightSpec(n["up"], ((F, H),)), WeightSpec(n["down"], ((H, F),))]
+
+    def bind(self, tensors):
+        self.w_up = tensors[self.names["up"]]
+        self.w_down = tensors[self.names["down"]]
+
+    def forward_into(self, x, out):
+        rt, T = self.rt, x.shape[0]
+        h = rt.workspace.get("ffn_h", (T, self.ff), rt.act_dtype, first="tokens")
+        ops.linear(x, self.w_up, h, status=rt.status)
+        ops.activation(h, h, self.act)
+        ops.linear(h, self.w_down, out, status=rt.status)
+
+    def forward(self, x, batch, residual, scale: float = 1.0):
+        if scale == 1.0:
+            rt, T = self.rt, x.shape[0]
+            h = rt.workspace.get("ffn_h", (T, self.ff), rt.act_dtype, first="tokens")
+            ops.linear(x, self.w_up, h, status=rt.status)
+            ops.activation(h, h, self.act)
+            ops.linear(h, self.w_down, residual, accumulate=True, status=rt.status)
+            return
+        out = self.rt.workspace.get("ffn_out", (x.shape[0], self.hidden), torch.float32, first="tokens")
+        self.forward_into(x, out)
+        ops.add_scaled(residual, out, scale)

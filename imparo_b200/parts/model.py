@@ -20,6 +20,9 @@ class Model:
         self.final_norm = make_part("norm", spec.final_norm, "", rt)
         self.head = make_part("head", spec.head, "", rt)
         self.schedule = spec.schedule
+        # what works on the stream right before a schedule entry (ScheduleEntry.before), by entry index
+        self.before: Dict[int, Part] = {i: make_part("stream_op", e.before, "", rt)
+                                        for i, e in enumerate(spec.schedule) if e.before is not None}
         self.graph_safe = all(p.graph_safe for p in self.parts())
         for i, e in enumerate(self.schedule):
             if e.cache_from is not None:
@@ -31,7 +34,7 @@ class Model:
 
     # -- weights -----------------------------------------------------------------------
     def parts(self) -> Sequence[Part]:
-        return [self.embedding, *self.layers, self.final_norm, self.head]
+        return [self.embedding, *self.layers, *self.before.values(), self.final_norm, self.head]
 
     def weight_specs(self) -> List[WeightSpec]:
         """Every tensor the model reads, once per name (a tied head names the embedding's)."""
@@ -73,6 +76,8 @@ class Model:
         last = len(self.schedule) - 1
         for i, e in enumerate(self.schedule):
             layer = self.layers[e.layer]
+            if i in self.before:
+                self.before[i].forward(x, batch)
             self.rt.probe_now = self.rt.probe is not None and self.rt.probe_entry == i
             if i == last and wanted is not None and wanted[1] < batch.n_tokens and layer.picks_rows:
                 out = layer.forward(x, batch, cache_views(i), only_rows=wanted)

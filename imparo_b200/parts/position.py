@@ -17,6 +17,11 @@ from .base import Part
 
 
 class PositionEncoding(Part):
+    # which dimensions make a rotation pair: False (i, i + n_rot/2), True (2i, 2i + 1)
+    interleaved = False
+    # a factor on every sine and cosine (1: a pure rotation)
+    magnitude = 1.0
+
     def rotary(self) -> Optional[Tuple[torch.Tensor, int]]:
         """(inv_freq float32 [n_rot/2] on the device, n_rot): dimension i < n_rot/2 pairs
         with i + n_rot/2 and turns by position * inv_freq[i].  None: no rotation."""
@@ -43,3 +48,45 @@ class RotaryNeox(PositionEncoding):
 
     def rotary(self):
         return self.inv_freq, self.n_rot
+
+
+class RotaryInterleaved(PositionEncoding):
+    """Rotation of the pairs (2i, 2i+1) over the first n_rot dimensions of a head, the rest passing unchanged;
+    frequency of pair i: theta^(-2i/n_rot).
+
+    params: head_dim, theta, n_rot (default head_dim), scaling (optional: factor, original, fast, slow).
+    With scaling, frequencies are blended between the plain one and the plain one divided by `factor`, by how many
+    turns a pair makes over `original` positions: with dim(t) = n_rot * ln(original / (2 pi t)) / (2 ln theta),
+    lo = max(floor(dim(fast)), 0), hi = min(ceil(dim(slow)), n_rot - 1) and
+    ramp_i = clamp((i - lo) / max(hi - lo, 0.001), 0, 1), pair i turns at f_i / factor * ramp_i + f_i * (1 - ramp_i);
+    and sines and cosines are multiplied by 0.1 * ln(factor) + 1.  The table is computed in 64-bit on the host and
+    kept in 32-bit; angles are position * frequency in 32-bit."""
+    interleaved = True
+
+    def __init__(self, params, prefix, rt):
+        super().__init__(params, prefix, rt)
+        self.head_dim = int(params["head_dim"])
+        self.n_rot = int(params.get("n_rot", self.head_dim))
+        self.theta = float(params["theta"])
+        if self.n_rot % 2 or not 0 <= self.n_rot <= self.head_dim:
+            raise ValueError(f"rotary: n_rot {self.n_rot} must be even and at most the head size {self.head_dim}")
+        self.inv_freq, self.magnitude = self.table(self.n_rot, self.theta, params.get("scaling"))
+        self.inv_freq = self.inv_freq.to(torch.float32).to(rt.device)
+
+    @staticmethod
+    def table(n_rot: int, theta: float, scaling=None):
+        """(frequencies float64 [n_rot/2], magnitude)."""
+        import math
+        i = torch.arange(n_rot // 2, dtype=torch.float64)
+        f = torch.pow(torch.tensor(theta, dtype=torch.float64), -2.0 * i / max(n_rot, 1))
+        if not scaling:
+            return f, 1.0
+        factor, original = float(scaling["factor"]), float(scaling["original"])
+        where = lambda turns: n_rot * math.log(original / (2.0 * math.pi * turns)) / (2.0 * math.log(theta))
+        lo = max(math.floor(where(float(scaling["fast"]))), 0)
+        hi = min(math.ceil(where(float(scaling["slow"]))), n_rot - 1)
+        ramp = torch.clamp((i - lo) / max(hi - lo, 0.001), 0.0, 1.0)
+        return f / factor * ramp + f * (1.0 - ramp), 0.1 * math.log(factor) + 1.0
+
+    def rotary(self):
+        return (self.inv_freq, self.n_rot) if self.n_rot else None

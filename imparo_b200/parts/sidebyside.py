@@ -1,0 +1,64 @@
+"""Several mixers that read the same input, as one mixer (mixer "side_by_side").
+
+Each branch is a mixer of its own (its own tensors under its own prefix, its own cache needs).  The result is the
+mean of the branches' outputs, each first RMS-normed over the model width with a plain weight of its own:
+
+    out = (1 / n) * sum_b  rms(branch_b(x)) * w_b
+
+added into the stream times `scale` (the arrangement's residual factor).  The branches write 32-bit buffers
+[tokens, hidden]; the norms, the mean and the add are one kernel.
+"""
+from __future__ import annotations
+
+import torch
+
+from ..kernels import ops
+from .base import Part, make_part
+from .spec import WeightSpec
+
+
+class SideBySideMixer(Part):
+    """params: hidden, eps, branches: a sequence of (sub-prefix, PartSpec of a mixer, name of its output-norm weight
+    after this part's prefix)."""
+    takes_scale = True
+
+    def __init__(self, params, prefix, rt):
+        super().__init__(params, prefix, rt)
+        self.hidden = int(params["hidden"])
+        self.eps = float(params["eps"])
+        self.branches = []
+        for sub, spec, norm_name in params["branches"]:
+            self.branches.append((make_part("mixer", spec, prefix + sub, rt), prefix + norm_name))
+        if not 1 <= len(self.branches) <= 4:
+            raise ValueError("side-by-side mixer: one to four branches")
+        self.graph_safe = all(b.graph_safe for b, _ in self.branches)
+        self.norm_w = []
+        self._n_caches = [len(b.cache_specs()) for b, _ in self.branches]
+
+    def weight_specs(self):
+        specs = []
+        for b, norm_name in self.branches:
+            specs += b.weight_specs()
+            specs.append(WeightSpec(norm_name, ((self.hidden,),), role="vector", init=("norm",)))
+        return specs
+
+    def bind(self, tensors):
+        self.norm_w = []
+        for b, norm_name in self.branches:
+            b.bind(tensors)
+            self.norm_w.append(tensors[norm_name])
+
+    def cache_specs(self):
+        return tuple(s for b, _ in self.branches for s in b.cache_specs())
+
+    def forward(self, x, batch, caches, residual, scale: float = 1.0, extra=None, extra_scale: float = 0.0):
+        """extra: a float32 [tokens, hidden] buffer added as well, times extra_scale, in the same pass over the
+        stream (the arrangement's other sublayer)."""
+        rt, T = self.rt, x.shape[0]
+        outs, at = [], 0
+        for i, (b, _) in enumerate(self.branches):
+            buf = rt.workspace.get(f"branch_out_{i}", (T, self.hidden), torch.float32, first="tokens")
+            b.forward(x, batch, caches[at:at + self._n_caches[i]], buf, accumulate=False)
+            at += self._n_caches[i]
+            outs.append(buf)
+        ops.norm_mean_add(residual, outs, self.norm_w, self.eps, scale / len(outs), extra, extra_scale)

@@ -29,18 +29,22 @@ class LayerSpec:
     """
     prefix: str
     mixer: PartSpec
-    feed_forward: PartSpec
+    feed_forward: Optional[PartSpec]          # None: the layer has no feed-forward (blocks that allow it)
     mixer_norm: PartSpec
-    feed_forward_norm: PartSpec
+    feed_forward_norm: Optional[PartSpec]     # None: the block has one norm that both sublayers read
     block: str = "prenorm_residual"
+    params: Mapping[str, Any] = field(default_factory=dict)      # the arrangement's own constants (e.g. residual_scale)
 
 
 @dataclass(frozen=True)
 class ScheduleEntry:
     """One run of a layer.  cache_from names an EARLIER entry of the schedule whose
-    cache this run reads instead of owning one (it then writes nothing there)."""
+    cache this run reads instead of owning one (it then writes nothing there).
+    before: a "stream_op" part that works on the residual stream right before this run (a vector added at
+    the start of a repeated stretch of layers, the embedding added again, ...)."""
     layer: int
     cache_from: Optional[int] = None
+    before: Optional[PartSpec] = None
 
 
 @dataclass(frozen=True)
@@ -85,10 +89,15 @@ class PagedKV:
     n_kv_heads: int
     head_dim: int
     window: Optional[int] = None
+    v_head_dim: Optional[int] = None        # None: values are as wide as keys
 
     @property
     def width(self) -> int:
         return self.n_kv_heads * self.head_dim
+
+    @property
+    def v_width(self) -> int:
+        return self.n_kv_heads * (self.head_dim if self.v_head_dim is None else self.v_head_dim)
 
 
 @dataclass(frozen=True)
