@@ -21,7 +21,7 @@ import time
 
 
 def build_parser() -> argparse.ArgumentParser:
-    ap = argparse.ArgumentParser(prog="python -m imparo_b200", description="LFM2 generation from token ids on one B200.")
+    ap = argparse.ArgumentParser(prog="python -m imparo_b200", description="Generation from token ids on one B200 (the architecture is the one config.json names).")
     ap.add_argument("-m", "--model", help="folder with config.json and model.safetensors")
     ap.add_argument("--random", metavar="CONFIG.json", help="random weights for this config.json instead of a model folder")
     ap.add_argument("--write-random", metavar="DIR", help="with --random: write the model folder DIR and exit")

@@ -663,7 +663,7 @@ extern "C" int imparo_attention_prefill(const void* q, const void* k_cache, cons
 
 // Implemented in attention_split.cu: the ordered combine of split partials.
 extern "C" int imparo_attention_split_combine(const float* part_acc, const float* part_ml, void* out, int dtype,
-                                              int n_rows, int hd, int n_splits, cudaStream_t stream);
+                                              int n_rows, int hd, int n_splits, int sink, cudaStream_t stream);
 
 // Single query tokens on tensor cores: bfloat16, head size 64 or 128, at most 8 query heads per
 // kv head; else -8.  Scratch as for imparo_paged_attention_split.  out == nullptr: the partials are
@@ -705,7 +705,7 @@ static int decode_mma_launch(const void* q, const pf::QkvSource* qkv_src, const 
 #undef IMPARO_DECODE
     if (e != cudaSuccess) return (int)e;
     if (out == nullptr) return 0;
-    return imparo_attention_split_combine(part_acc, part_ml, out, IMPARO_DT_BF16, n_tok * nh, hd, n_splits, stream);
+    return imparo_attention_split_combine(part_acc, part_ml, out, IMPARO_DT_BF16, n_tok * nh, hd, n_splits, 0, stream);
 }
 
 extern "C" int imparo_attention_decode_mma(const void* q, const void* k_cache, const void* v_cache,

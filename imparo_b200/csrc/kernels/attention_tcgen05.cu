@@ -86,6 +86,8 @@ struct Args {
     int n_items, max_blocks, page_size, n_pages, window, nh, nkv;
     float scale;
     int late_trigger;        // the next kernel runs beside this one and must find all before this one complete (common.cuh)
+    int sink;                // the softmax's denominator counts one more term of score 0 that has no value: the running max
+                             // starts at 0 and the running sum at 1, as if a key of score 0 had been seen before all others
 };
 
 template <int HD>
@@ -279,7 +281,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
         float o[DH];
 #pragma unroll
         for (int d = 0; d < DH; ++d) o[d] = 0.f;
-        float m_run = -INFINITY, l_run = 0.f, corr_prev = 0.f;
+        float m_run = a.sink ? 0.f : -INFINITY, l_run = (a.sink && half == 0) ? 1.f : 0.f, corr_prev = 0.f;
         const float sl2 = a.scale * 1.4426950408889634f;     // scores in units of log2(e)
         bool ok = true;
         auto fold_pv = [&](float corr) {                     // o = o * corr + O_step (this thread's dims)
@@ -747,7 +749,7 @@ attn_prefill_pp_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             mbar_arrive(q_ready);
         }
-        float m_used = -INFINITY, l_run = 0.f;
+        float m_used = -INFINITY, l_run = (a.sink && half == 0) ? 1.f : 0.f;       // (the sink's 1 is in units of max 0: see j == 0)
         const float sl2 = a.scale * 1.4426950408889634f;     // scores in units of log2(e)
         bool ok = true;
         uint8_t* prow = p_s + x * P_BYTES + half * REGION + r * 128;         // keys 0-63 and 64-127 are the two blocks of P
@@ -798,7 +800,8 @@ attn_prefill_pp_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
             // the max in use stays unless it would be exceeded by more than PP_GROW somewhere in the warp
             float m_new, corr = 1.f;
             if (j == 0) {
-                m_new = m_row;
+                m_new = a.sink ? fmaxf(m_row, 0.f) : m_row;
+                if (a.sink) corr = ex2(-m_new);                              // the sink's share of the sum, brought to the max in use
             } else {
                 const bool grow = m_row > m_used + PP_GROW;                  // (true for m_used = -inf and a finite m_row)
                 const bool rescale = __any_sync(0xffffffffu, grow);
@@ -964,6 +967,7 @@ extern "C" int imparo_attention_prefill_tc(const void* q, const void* k_cache, c
     a.n_items = n_items; a.max_blocks = max_blocks; a.page_size = page_size; a.n_pages = n_pages; a.window = window;
     a.nh = nh; a.nkv = nkv; a.scale = scale;
     a.late_trigger = (mode >> 1) & 1;
+    a.sink = (mode >> 2) & 1;
     if (hd == 64 && two_tiles) {
         // two tiles per CTA: half as many CTAs along y (an upper bound again)
         const long long pairs = (n_tok + 2 * TQ - 1) / (2 * TQ) + n_items;

@@ -86,7 +86,7 @@ def _declare_kernels(lib):
              [P, P, P, I, P, P, P, I, I, I, I, c_float, P, I, I, I, I, P, S])
     _declare(lib, "imparo_paged_attention_split",
              [P, P, P, I, P, P, P, I, I, I, I, c_float, P, P, P, I, I, I, I, I, I, P, S])
-    _declare(lib, "imparo_attention_split_combine", [P, P, P, I, I, I, I, S])
+    _declare(lib, "imparo_attention_split_combine", [P, P, P, I, I, I, I, I, S])
     _declare(lib, "imparo_attention_decode_mma",
              [P, P, P, P, P, P, I, I, I, I, c_float, P, P, P, I, I, I, I, I, I, I, I, P, S])
     _declare(lib, "imparo_attention_decode_mma_qkv",
@@ -114,6 +114,7 @@ def _declare_kernels(lib):
     _declare(lib, "imparo_qkv_rotate_store", [P, I, P, P, P, I, I, c_float, P, P, P, P, I, I, I, I, I, I, I, I, P, S])
     _declare(lib, "imparo_attention_any", [P, P, P, I, P, P, P, I, I, I, I, c_float, I, P, I, I, I, I, I, P, S])
     _declare(lib, "imparo_linear_attention_recurrent", [P, P, P, c_int64, I, I, P, P, P, P, I, I, P, I, I, I, P, S])
+    _declare(lib, "imparo_linear_attention_chunked", [P, P, P, c_int64, I, I, P, P, P, I, I, P, P, I, I, P, I, I, I, P, S])
 
 
 def _declare_host(lib):

@@ -619,11 +619,12 @@ def linear_of_attention_partials(part_acc, part_ml, n_tok, nh, hd, n_splits, w_o
     return True
 
 
-def attention_split_combine(part_acc, part_ml, out, n_rows, hd, n_splits) -> None:
-    """The ordered combine alone: out[row, :] from the partials of paged_attention_split(out=None)."""
+def attention_split_combine(part_acc, part_ml, out, n_rows, hd, n_splits, sink: bool = False) -> None:
+    """The ordered combine alone: out[row, :] from the partials of paged_attention_split(out=None).  sink: the softmax's
+    denominator counts one more term of score 0 that has no value."""
     _cuda(part_acc, part_ml, out)
     _check(_lib.kernels().imparo_attention_split_combine(_ptr(part_acc), _ptr(part_ml), _ptr(out), _code(out), n_rows, hd,
-                                                         n_splits, _stream()), "attention_split_combine")
+                                                         n_splits, int(bool(sink)), _stream()), "attention_split_combine")
 
 
 def _parts_of(x):
@@ -715,7 +716,7 @@ def split_plan(n_tok: int, nkv: int, upper_context: int, sms: Optional[int] = No
 
 def paged_attention_split(q, k_cache, v_cache, positions, item_of_token, table, page_size, n_pages, window, scale,
                           out, part_acc, part_ml, chunk, n_splits, nh, nkv, hd, status, mma: bool = True,
-                          fresh: int = 0, overlap_prev: bool = False) -> bool:
+                          fresh: int = 0, overlap_prev: bool = False, sink: bool = False) -> bool:
     """Split-key attention (one CTA per key chunk, kv head and query token, then an ordered
     combine).  Returns False, having launched nothing, when the group size is above 8.
 
@@ -729,9 +730,20 @@ def paged_attention_split(q, k_cache, v_cache, positions, item_of_token, table, 
 
     overlap_prev: the kernel launched just before this one was attention_prefill with dependents_after_wait and
     returned 2, and it neither writes what this launch reads nor reads what it writes: the tensor-core kernel then
-    runs beside it instead of after it (and completes after it)."""
+    runs beside it instead of after it (and completes after it).
+
+    sink: the softmax's denominator counts one more term of score 0 that has no value; it enters in the combine, so
+    the partials are left uncombined by the first kernel and the combine runs as a launch of its own (out is needed)."""
     if nh // nkv > 8:
         return False
+    if sink:
+        _need(out is not None, "paged_attention_split: a sink is added by the combine, which needs out")
+        ok = paged_attention_split(q, k_cache, v_cache, positions, item_of_token, table, page_size, n_pages, window, scale,
+                                   None, part_acc, part_ml, chunk, n_splits, nh, nkv, hd, status, mma=mma, fresh=fresh,
+                                   overlap_prev=overlap_prev)
+        if ok:
+            attention_split_combine(part_acc, part_ml, out, q.shape[0] * nh, hd, n_splits, sink=True)
+        return ok
     _cuda(q, k_cache, v_cache, positions, item_of_token, table, out, part_acc, part_ml, status)
     use_mma = mma and q.dtype == torch.bfloat16 and hd in (64, 128) and chunk >= 64
     T = q.shape[0]
@@ -803,7 +815,8 @@ def attention_decode_from_qkv(qkv, positions, item_of_token, q_w, k_w, inv_freq,
 
 
 def attention_prefill(q, k_cache, v_cache, item_row_start, item_start_pos, n_items, table, page_size, n_pages, window,
-                      scale, out, nh, nkv, hd, status, kernel: str = "auto", dependents_after_wait: bool = False):
+                      scale, out, nh, nkv, hd, status, kernel: str = "auto", dependents_after_wait: bool = False,
+                      sink: bool = False):
     """Tensor-core attention for prompt portions (bfloat16, head size 64 or 128, at most 8
     query heads per kv head).  Returns False, having launched nothing, for other shapes.
 
@@ -813,8 +826,13 @@ def attention_prefill(q, k_cache, v_cache, item_row_start, item_start_pos, n_ite
     kernel: "tcgen05" (TMA + tcgen05.mma with the scores in tensor memory; pages of 16, 32, 64 or
     128 positions; at head size 64 a CTA takes two query tiles in turn), "tcgen05_one_tile" (the same with one tile
     per CTA at every head size), "mma" (mma.sync, any page size), or "auto": the first where it takes the shape
-    (IMPARO_ATTN_PREFILL=mma in the environment makes "auto" skip it)."""
+    (IMPARO_ATTN_PREFILL=mma in the environment makes "auto" skip it).
+
+    sink: the softmax's denominator counts one more term of score 0 that has no value (the tcgen05 kernels only;
+    where they decline the result is False)."""
     if q.dtype != torch.bfloat16 or hd not in (64, 128) or nh // nkv > 8:
+        return False
+    if sink and kernel == "auto" and _S.switches.attn_prefill == "mma":
         return False
     _cuda(q, k_cache, v_cache, item_row_start, item_start_pos, table, out, status)
     T = q.shape[0]
@@ -836,12 +854,15 @@ def attention_prefill(q, k_cache, v_cache, item_row_start, item_start_pos, n_ite
         # part of the step's shape
         two_tiles = kernel == "tcgen05" or (kernel == "auto" and table.shape[1] * page_size >= 1024)
         late = bool(dependents_after_wait)      # without programmatic launches the two kernels simply run in stream order
-        rc = _lib.kernels().imparo_attention_prefill_tc(*args[:-2], (1 if two_tiles else 0) | (2 if late else 0), *args[-2:])
+        rc = _lib.kernels().imparo_attention_prefill_tc(*args[:-2], (1 if two_tiles else 0) | (2 if late else 0) | (4 if sink else 0),
+                                                        *args[-2:])
         if rc != -8:
             _check(rc, "attention_prefill_tc")
             return 2 if late else True
-        if kernel != "auto":
+        if kernel != "auto" or sink:
             return False
+    if sink:
+        return False
     _check(_lib.kernels().imparo_attention_prefill(*args), "attention_prefill")
     return True
 
@@ -1047,10 +1068,16 @@ def attention_any(q, k_cache, v_cache, positions, item_of_token, table, page_siz
 # ---- linear attention with decay (csrc/kernels/linear_attention.cu) -------------------------------------------
 def linear_attention(qkv: torch.Tensor, q_off: int, k_off: int, v_off: int, decay: torch.Tensor, state: torch.Tensor,
                      item_row_start, item_slot, n_items: int, out: torch.Tensor, heads: int, dim: int, vdim: int,
-                     status: torch.Tensor, act: Optional[str] = "silu") -> None:
+                     status: torch.Tensor, act: Optional[str] = "silu", chunk: int = 0,
+                     chunk_state: Optional[torch.Tensor] = None) -> None:
     """Per request and head: S = decay * S + k v^T, o = S^T q over the request's rows in order, from and into
     state[slot].  qkv: [T, width] rows holding q (heads*dim) at column q_off, k at k_off, v (heads*vdim) at v_off;
-    act: "silu" or None, applied to q, k and v.  state: float32 [slots, heads, dim, vdim]; out: float32 [T, heads*vdim]."""
+    act: "silu" or None, applied to q, k and v.  state: float32 [slots, heads, dim, vdim]; out: float32 [T, heads*vdim].
+
+    chunk > 0 (batches with long portions): the rows of a request are cut into chunks of that many rows which run side by
+    side (three launches: every chunk's own sum, a scan over each request's chunks, every chunk's outputs); chunk_state is
+    float32 scratch for (T // chunk + n_items) * heads * dim * vdim values.  The result differs from the row-by-row walk
+    by the order of 32-bit additions only."""
     _need(qkv.is_cuda and qkv.stride(1) == 1, "kernels run on CUDA tensors only (there is no CPU path)")
     _cuda(decay, state, item_row_start, item_slot, out, status)
     T = qkv.shape[0]
@@ -1062,6 +1089,17 @@ def linear_attention(qkv: torch.Tensor, q_off: int, k_off: int, v_off: int, deca
     _need(item_row_start.numel() >= n_items + 1 and item_slot.numel() >= n_items, "linear_attention: item arrays")
     es = qkv.element_size()
     base = qkv.data_ptr()
+    if chunk > 0:
+        max_chunks = T // chunk + n_items
+        _cuda(chunk_state)
+        _need(chunk_state is not None and chunk_state.dtype == torch.float32
+              and chunk_state.numel() >= max_chunks * heads * dim * vdim, "linear_attention: chunk_state scratch too small")
+        _check(_lib.kernels().imparo_linear_attention_chunked(
+            base + q_off * es, base + k_off * es, base + v_off * es, qkv.stride(0), _code(qkv), int(act == "silu"), _ptr(decay),
+            _ptr(state), _ptr(chunk_state), int(chunk), int(max_chunks), _ptr(item_row_start), _ptr(item_slot), int(n_items),
+            state.shape[0], _ptr(out), heads, dim, vdim, _ptr(status), _stream()), "linear_attention_chunked")
+        COUNTS["own"] += 2
+        return
     _check(_lib.kernels().imparo_linear_attention_recurrent(
         base + q_off * es, base + k_off * es, base + v_off * es, qkv.stride(0), _code(qkv), int(act == "silu"), _ptr(decay),
         _ptr(state), _ptr(item_row_start), _ptr(item_slot), int(n_items), state.shape[0], _ptr(out), heads, dim, vdim,

@@ -21,6 +21,7 @@ class DecayLinearAttention(Part):
 
     forward(..., accumulate=False) overwrites `residual` (then any float32 [tokens, hidden] buffer)."""
     adds_with_linear = True
+    CHUNK_FROM = 128          # portions from this many tokens on (rounded up to a power of two) run in chunks
 
     NAMES = {"q": "q", "k": "k", "v": "v", "g": "g", "o": "o", "norm": "norm"}
 
@@ -66,8 +67,15 @@ class DecayLinearAttention(Part):
         proj = rt.workspace.get("linattn_in", (T, 2 * qk + 2 * vv), rt.act_dtype, first="tokens")
         ops.linear(x, self.w_in, proj, status=rt.status)
         o = rt.workspace.get("linattn_o", (T, vv), torch.float32, first="tokens")
+        # long portions: the recurrence in chunks that run side by side (a row-by-row walk of a 2,048-token prompt is 2,048
+        # dependent steps on a handful of warps); the chunk length follows the step's size, which is part of its shape
+        chunk, scratch = 0, None
+        if batch.max_tokens_per_item >= self.CHUNK_FROM:
+            chunk = 64 if T <= 4096 else (128 if T <= 16384 else 256)
+            scratch = rt.workspace.get("linattn_chunks", ((T // chunk + batch.n_items) * self.heads * self.dim * self.vdim,),
+                                       torch.float32)
         ops.linear_attention(proj, 0, qk, 2 * qk, self.decay, st.state, batch.item_row_start, batch.item_slot, batch.n_items,
-                             o, self.heads, self.dim, self.vdim, rt.status, act=self.act)
+                             o, self.heads, self.dim, self.vdim, rt.status, act=self.act, chunk=chunk, chunk_state=scratch)
         y = rt.workspace.get("linattn_y", (T, vv), rt.act_dtype, first="tokens")
         ops.gated_rmsnorm(o, self.w_norm, self.eps, proj[:, 2 * qk + vv:], y)
         ops.linear(y, self.w_o, residual, accumulate=accumulate, status=rt.status)

@@ -1,0 +1,549 @@
+"""Vipotar on the GPU against the plain implementation (tests/plain/vipotar_plain.py), in 32-bit and bfloat16:
+each mechanism's kernel alone, the replay families (whole, last tokens one by one, portions down to two tokens,
+mixed batches with pages and slots used again), keys at window and page borders made to stand out, far keys
+carried by the recurrent state, the first tokens of a sequence, long decoding, and greedy generation through
+Engine.generate and the command line."""
+import functools
+import json
+import os
+import subprocess
+import sys
+import tempfile
+
+import numpy as np
+import pytest
+
+from tests import traces
+from tests.plain import vipotar_plain as P
+from tests.plain.lfm2_plain import read_safetensors
+from tests.vipotar_configs import ALL, PAGE
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+# Fractions of the largest |logit| of the compared requests.  float32 is the sharp test: every position within 3e-5.
+# bfloat16: the design norms each mixer's output (scale-free), so where a tiny model's output hangs on one or two small
+# dot products (the first positions of a sequence above all) the rounding of the projections to 8 bits is amplified; nine
+# positions in ten stay within 3e-2 and none leaves 0.2 (a wrong key, window or state moves a position by the scale itself).
+TOL = {"float32": 3e-5, "bfloat16": 3e-2}
+WORST = {"float32": 3e-5, "bfloat16": 0.2}
+
+
+def all_errors(steps, got, want):
+    """[(step, request, position, max abs error)] for every wanted place."""
+    at, out = {}, []
+    for s in steps:
+        r = 0
+        for e in s["entries"]:
+            start = at.get(e["id"], 0)
+            for w in e["want"]:
+                out.append((s["step"], e["id"], start + w, float(np.abs(got[s["step"]][r] - want[s["step"]][r]).max())))
+                r += 1
+            at[e["id"]] = start + len(e["tokens"])
+        for name in s["end"]:
+            at.pop(name, None)
+    return out
+_tmp = tempfile.TemporaryDirectory(prefix="imparo_b200_vipotar_")
+
+
+@functools.lru_cache(maxsize=None)
+def model_dir(name, seed=1):
+    from imparo_b200.weights import write_random_model
+    d = os.path.join(_tmp.name, f"{name}_{seed}")
+    # matrices wide enough that scores, gates and activations are not all near zero
+    write_random_model(d, ALL[name], seed=seed, dtype="bfloat16", matrix_std=0.12, norm_jitter=0.3)
+    return d
+
+
+@functools.lru_cache(maxsize=None)
+def weights(name, seed=1):
+    return read_safetensors(os.path.join(model_dir(name, seed), "model.safetensors"))
+
+
+def make_requests(name, lengths, seed=0):
+    rng = np.random.default_rng(seed)
+    return {f"r{i}": rng.integers(0, ALL[name]["vocab"], n).tolist() for i, n in enumerate(lengths)}
+
+
+_plain = {}
+
+
+def plain_logits(name, requests, seed=1):
+    out = {}
+    for rid, toks in requests.items():
+        key = (name, seed, tuple(toks))
+        if key not in _plain:
+            _plain[key] = P.forward(ALL[name], weights(name, seed), toks)
+        out[rid] = _plain[key]
+    return out
+
+
+def engine_for(name, dtype, steps, parallel=4, **kw):
+    from imparo_b200.engine import Engine
+    page = PAGE[name]
+    max_tokens = traces.max_live_tokens(steps, 64)
+    return Engine(model_dir(name), dtype=dtype, ctx=max_tokens, parallel=parallel, page_size=page,
+                  num_pages=(max_tokens + page - 1) // page, max_step_tokens=max(256, max_tokens), **kw)
+
+
+def check_trace(engine, steps, name, requests, dtype, share=0.1):
+    from tests.gpu_helpers import run_trace
+    ref = plain_logits(name, requests)
+    want = traces.expected(steps, ref)
+    got = run_trace(engine, steps)
+    assert sorted(got) == sorted(want)
+    scale = max(float(np.abs(v).max()) for v in ref.values())
+    errs = all_errors(steps, got, want)
+    bad = next((e for e in errs if not e[3] <= WORST[dtype] * scale), None)
+    assert bad is None, (f"first wrong place: step {bad[0]}, request {bad[1]}, position {bad[2]}, "
+                         f"error {bad[3]:.3e} > {WORST[dtype] * scale:.3e}")
+    over = [e for e in errs if not e[3] <= TOL[dtype] * scale]
+    assert len(over) <= share * len(errs), (f"{len(over)} of {len(errs)} places beyond {TOL[dtype] * scale:.3e}; the first: {over[0]}")
+    assert engine.cache.n_requests() == 0
+    return got
+
+
+LENGTHS = {"A": [70, 45, 96, 33, 64, 51], "B": [5, 23, 40, 67, 90, 34], "C": [81, 40, 65, 97, 58], "D": [44, 71, 36, 60],
+           "E": [150, 47, 96, 201, 64], "F": [130, 75, 40, 164]}
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", sorted(ALL))
+@pytest.mark.parametrize("family", ["whole", "tail", "portions", "mixed"])
+def test_family(name, dtype, family):
+    reqs = make_requests(name, LENGTHS[name])
+    steps = {"whole": traces.whole, "tail": traces.tail_one_by_one, "portions": traces.portions,
+             "mixed": lambda r: traces.mixed(r, seed=3)}[family](reqs)
+    check_trace(engine_for(name, dtype, steps), steps, name, reqs, dtype)
+    if family == "mixed":
+        assert traces.max_live_tokens(steps) < sum(traces.round_up(len(t), 64) for t in reqs.values())
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["A", "E"])
+def test_cutting_does_not_change_logits_beyond_rounding(name, dtype):
+    from tests.gpu_helpers import run_trace
+    reqs = make_requests(name, [61, 47, 75], seed=5)
+    outs = []
+    for build in (traces.whole, traces.tail_one_by_one, traces.portions, lambda r: traces.mixed(r, seed=9)):
+        steps = build(reqs)
+        got = run_trace(engine_for(name, dtype, steps), steps)
+        by_pos, at = {}, {}
+        for s in steps:
+            r = 0
+            for e in s["entries"]:
+                start = at.get(e["id"], 0)
+                for w in e["want"]:
+                    by_pos[(e["id"], start + w)] = got[s["step"]][r]
+                    r += 1
+                at[e["id"]] = start + len(e["tokens"])
+        outs.append(by_pos)
+    keys = set(outs[1]) & set(outs[0])
+    assert len(keys) > 90
+    scale = max(float(np.abs(v).max()) for v in outs[0].values())
+    tol = (2e-5 if dtype == "float32" else 0.2) * scale
+    for k in keys:
+        for o in outs[1:]:
+            if k in o:
+                assert np.abs(o[k] - outs[0][k]).max() <= tol, k
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["B", "E", "F"])
+def test_long_portions(name, dtype):
+    """Prompts of several hundred tokens, whole and in portions of 128 to 300 tokens beside another request's single
+    tokens: the linear attention runs in chunks side by side, the attention on whole query tiles (E, F in bfloat16)."""
+    reqs = make_requests(name, [700, 333], seed=13)
+    steps = traces.whole(reqs)
+    check_trace(engine_for(name, dtype, steps), steps, name, reqs, dtype)
+    a, b = reqs["r0"], reqs["r1"]
+    steps, at_a, at_b = [], 0, 0
+    steps.append({"step": 0, "entries": [{"id": "b", "tokens": b[:300], "want": [0, 150, 299]}], "end": []})
+    at_b = 300
+    for n in (300, 129, 200, 71):
+        steps.append({"step": len(steps), "entries": [{"id": "a", "tokens": a[at_a:at_a + n], "want": [0, n // 2, n - 1]},
+                                                     {"id": "b", "tokens": [b[at_b]], "want": [0]}],
+                      "end": ["a"] if at_a + n == 700 else []})
+        at_a += n
+        at_b += 1
+    steps.append({"step": len(steps), "entries": [{"id": "b", "tokens": b[at_b:], "want": [0, len(b) - at_b - 1]}], "end": ["b"]})
+    check_trace(engine_for(name, dtype, steps), steps, name, {"a": a, "b": b}, dtype)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["A", "C"])
+def test_long_decoding(name, dtype):
+    """390 tokens one by one: the window passes over decoded tokens many times, pages behind it are given back,
+    the recurrent state carries the start of the prompt (decays up to 0.999)."""
+    reqs = make_requests(name, [400], seed=8)
+    steps = traces.tail_one_by_one(reqs, tail=390)
+    check_trace(engine_for(name, dtype, steps), steps, name, reqs, dtype)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["A", "B", "C"])
+def test_first_tokens_of_a_sequence(name, dtype):
+    reqs = make_requests(name, [1, 2, 3, 6], seed=11)
+    for build in (traces.whole, lambda r: traces.tail_one_by_one(r, tail=8)):
+        steps = build(reqs)
+        # (the first positions are where bfloat16 rounding is amplified most: only the outer bound holds for all of them)
+        check_trace(engine_for(name, dtype, steps), steps, name, reqs, dtype, share=1.0 if dtype == "bfloat16" else 0.0)
+
+
+@pytest.mark.parametrize("name", ["B", "E"])
+def test_state_slots_and_pages_start_clean_when_used_again(name):
+    a = make_requests(name, [50], seed=20)
+    b = {"other": make_requests(name, [37], seed=21)["r0"]}
+    steps = traces.whole(a) + [dict(s, step=s["step"] + 1) for s in traces.portions(b, sizes=(1, 2, 3))]
+    eng = engine_for(name, "float32", steps, parallel=1)       # one slot: it must be reused
+    check_trace(eng, steps, name, dict(a, **b), "float32")
+
+
+# ---- each mechanism's kernel alone ------------------------------------------------------------------------------
+
+def _dev(a, dtype=None):
+    import torch
+    t = torch.as_tensor(np.ascontiguousarray(a)).cuda()
+    return t if dtype is None else t.to(dtype)
+
+
+def _bf16_round(a):
+    import torch
+    return torch.as_tensor(np.asarray(a, dtype=np.float32)).to(torch.bfloat16).float().numpy().astype(np.float64)
+
+
+def _one_request_batch(T, page, start=0, n_pages=None):
+    """Device arrays of a batch with one request that brings T tokens from position `start`, its pages in reverse
+    order (a table that is no identity)."""
+    import torch
+    n_blocks = -(-(start + T) // page)
+    n_pages = n_pages or n_blocks + 3
+    table = np.full((1, n_blocks), -1, dtype=np.int32)
+    table[0] = np.arange(n_pages - 1, n_pages - 1 - n_blocks, -1)
+    pos = np.arange(start, start + T, dtype=np.int32)
+    return _dev(pos), _dev(np.zeros(T, dtype=np.int32)), _dev(table), n_pages
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("nh,nkv,hd,vd,n_rot,window,scaled", [(4, 2, 16, 24, 8, 9, True), (6, 1, 24, 8, 0, None, False),
+                                                              (3, 3, 32, 32, 32, 33, False), (8, 1, 96, 64, 48, 20, True),
+                                                              (2, 1, 40, 200, 6, 7, False)])
+def test_rotation_window_and_sink_kernels(dtype, nh, nkv, hd, vd, n_rot, window, scaled):
+    """qkv_rotate_store + attention_any against the plain attention: a prompt of 45 tokens, then 30 tokens one by one
+    on the same cache (pages of 4: every border is crossed), sink on."""
+    import torch
+    from imparo_b200.kernels import ops
+    from imparo_b200.parts.position import RotaryInterleaved
+    tdt = torch.float32 if dtype == "float32" else torch.bfloat16
+    rng = np.random.default_rng(hd + vd)
+    T, page, W = 75, 4, 8
+    rot = None
+    if n_rot:
+        rot = {"dims": n_rot, "base": 300.0}
+        if scaled:
+            rot["scaling"] = {"factor": 4.0, "original": 32, "fast": 8.0, "slow": 1.0}
+    cfg = {"heads": nh, "kv_heads": nkv, "dim": hd, "vdim": vd, "scale": 0.35}
+    if window:
+        cfg["mask"] = {"size": window}
+    if rot:
+        cfg["rot"] = rot
+    qkv = rng.standard_normal((T, nh * hd + nkv * (hd + vd)))
+    if dtype == "bfloat16":
+        qkv = _bf16_round(qkv)
+    # the plain attention takes projections: identity-like weights that pick q, k, v out of the row
+    width = qkv.shape[1]
+    eye = np.eye(width)
+    w = {"q": eye[:nh * hd], "k": eye[nh * hd:nh * hd + nkv * hd], "v": eye[nh * hd + nkv * hd:], "o": np.eye(nh * vd)}
+    want = P.window_attention(qkv, w, "", cfg, np.float64)
+    inv_freq, mag = (None, 1.0)
+    if rot:
+        f, mag = RotaryInterleaved.table(n_rot, rot["base"], rot.get("scaling"))
+        inv_freq = f.to(torch.float32).cuda()
+    status = ops.new_status("cuda")
+    n_pages_total = -(-T // page) + 3
+    kc = torch.zeros(n_pages_total * page * nkv * hd, dtype=tdt, device="cuda")
+    vc = torch.zeros(n_pages_total * page * nkv * vd, dtype=tdt, device="cuda")
+    got = np.zeros((T, nh * vd))
+    at = 0
+    for n in [45] + [1] * 30:
+        pos, iot, table, n_pages = _one_request_batch(n, page, start=at, n_pages=n_pages_total)
+        table_full = torch.full((1, -(-T // page)), -1, dtype=torch.int32, device="cuda")
+        table_full[0, :table.shape[1]] = torch.arange(n_pages_total - 1, n_pages_total - 1 - table.shape[1], -1, dtype=torch.int32)
+        x = _dev(qkv[at:at + n], tdt)
+        q = torch.empty(n, nh * hd, dtype=tdt, device="cuda")
+        out = torch.empty(n, nh * vd, dtype=tdt, device="cuda")
+        ops.qkv_rotate_store(x, pos, iot, inv_freq, n_rot, True, mag, q, kc, vc, table_full, page, n_pages_total, nh, nkv, hd, vd, status)
+        ops.attention_any(q, kc, vc, pos, iot, table_full, page, n_pages_total, window, cfg["scale"], True, out, nh, nkv, hd, vd, status)
+        got[at:at + n] = out.float().cpu().numpy()
+        at += n
+    ops.read_status(status)
+    scale = np.abs(want).max()
+    assert np.abs(got - want).max() <= (2e-5 if dtype == "float32" else 2.5e-2) * scale
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("heads,dim,vdim,decay", [(2, 8, 16, (0.9, 0.99)), (3, 16, 40, (0.5, 0.95, 1.0)), (1, 40, 72, (0.999,)),
+                                                  (2, 64, 64, (0.9, 0.995)), (1, 128, 128, (0.98,)), (1, 200, 33, (0.7,))])
+def test_decayed_linear_attention_kernel(dtype, heads, dim, vdim, decay):
+    """Three requests of unequal length in one launch, then their next portions and single tokens from the states the
+    first launch left, slots in no particular order; against the plain recurrence on each whole sequence."""
+    import torch
+    from imparo_b200.kernels import ops
+    tdt = torch.float32 if dtype == "float32" else torch.bfloat16
+    rng = np.random.default_rng(dim * 7 + vdim)
+    lens = [37, 5, 64]
+    qk, vv = heads * dim, heads * vdim
+    rows = [rng.standard_normal((n, 2 * qk + vv + 3)) * 0.7 for n in lens]          # three columns the kernel must skip
+    if dtype == "bfloat16":
+        rows = [_bf16_round(r) for r in rows]
+    want = []
+    for r in rows:
+        q, k, v = P.silu(r[:, 3:3 + qk]), P.silu(r[:, 3 + qk:3 + 2 * qk]), P.silu(r[:, 3 + 2 * qk:])
+        S = np.zeros((heads, dim, vdim))
+        o = np.zeros((len(r), vv))
+        for t in range(len(r)):
+            S = np.asarray(decay)[:, None, None] * S + k[t].reshape(heads, dim)[:, :, None] * v[t].reshape(heads, vdim)[:, None, :]
+            o[t] = np.einsum("hdv,hd->hv", S, q[t].reshape(heads, dim)).reshape(-1)
+        want.append(o)
+    slots = [4, 0, 2]
+    state = torch.full((6, heads, dim, vdim), 7.0, device="cuda")                     # stale values in every slot
+    state[slots] = 0.0
+    status = ops.new_status("cuda")
+    dec = torch.tensor(decay, dtype=torch.float32, device="cuda")
+    got = [np.zeros_like(w) for w in want]
+    at = [0, 0, 0]
+    for cut in ([20, 2, 31], [16, 1, 2], [1, 1, 1], [0, 1, 30]):
+        items = [i for i in range(3) if cut[i]]
+        x = np.concatenate([rows[i][at[i]:at[i] + cut[i]] for i in items])
+        starts = np.concatenate([[0], np.cumsum([cut[i] for i in items])]).astype(np.int32)
+        out = torch.empty(len(x), vv, device="cuda")
+        ops.linear_attention(_dev(x, tdt), 3, 3 + qk, 3 + 2 * qk, dec, state, _dev(starts), _dev(np.array([slots[i] for i in items], dtype=np.int32)),
+                             len(items), out, heads, dim, vdim, status)
+        o = out.cpu().numpy()
+        for j, i in enumerate(items):
+            got[i][at[i]:at[i] + cut[i]] = o[starts[j]:starts[j + 1]]
+            at[i] += cut[i]
+    ops.read_status(status)
+    assert at == lens
+    assert float(state[1].min()) == 7.0 and float(state[5].max()) == 7.0           # other slots untouched
+    for g, w in zip(got, want):
+        assert np.abs(g - w).max() <= 1e-5 * max(np.abs(w).max(), 1.0)
+    # the same rows in chunks that run side by side (chunks of 8 and of 16 rows; the requests' lengths are no multiples),
+    # first portions from fresh states, then the rest from the states those left
+    final = state[slots].cpu().numpy()
+    for chunk in (8, 16):
+        state[slots] = 0.0
+        got2 = [np.zeros_like(w) for w in want]
+        at = [0, 0, 0]
+        for cut in ([30, 3, 41], [7, 2, 23]):
+            x = np.concatenate([rows[i][at[i]:at[i] + cut[i]] for i in range(3)])
+            starts = np.concatenate([[0], np.cumsum(cut)]).astype(np.int32)
+            out = torch.empty(len(x), vv, device="cuda")
+            scratch = torch.full(((len(x) // chunk + 3) * heads * dim * vdim,), float("nan"), device="cuda")
+            ops.linear_attention(_dev(x, tdt), 3, 3 + qk, 3 + 2 * qk, dec, state, _dev(starts), _dev(np.array(slots, dtype=np.int32)), 3, out,
+                                 heads, dim, vdim, status, chunk=chunk, chunk_state=scratch)
+            o = out.cpu().numpy()
+            for i in range(3):
+                got2[i][at[i]:at[i] + cut[i]] = o[starts[i]:starts[i + 1]]
+                at[i] += cut[i]
+        ops.read_status(status)
+        assert at == lens
+        for g, w in zip(got2, want):
+            assert np.abs(g - w).max() <= 1e-5 * max(np.abs(w).max(), 1.0)
+        assert np.abs(state[slots].cpu().numpy() - final).max() <= 1e-5 * max(np.abs(final).max(), 1.0)
+        assert float(state[1].min()) == 7.0 and float(state[5].max()) == 7.0
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_row_kernels(dtype):
+    """Gated norm, mean of normed branches with the other sublayer added, activations, soft cap, stream injection."""
+    import torch
+    from imparo_b200.kernels import ops
+    tdt = torch.float32 if dtype == "float32" else torch.bfloat16
+    rng = np.random.default_rng(4)
+    T, W = 19, 100
+    tol = 1e-5 if dtype == "float32" else 1e-2
+    o, wn = rng.standard_normal((T, W)), rng.standard_normal(W)
+    gate = rng.standard_normal((T, W + 5))
+    gate_r = gate if dtype == "float32" else _bf16_round(gate)
+    out = torch.empty(T, W, dtype=tdt, device="cuda")
+    ops.gated_rmsnorm(_dev(o, torch.float32), _dev(wn, torch.float32), 1e-5, _dev(gate_r, tdt)[:, 5:], out)
+    want = P.rms_norm(o, wn, 1e-5) * P.sigmoid(gate_r[:, 5:])
+    assert np.abs(out.float().cpu().numpy() - want).max() <= tol * np.abs(want).max()
+    x = rng.standard_normal((T, W))
+    br = [rng.standard_normal((T, W)) * s for s in (0.1, 30.0, 1.0)]
+    ws = [rng.standard_normal(W) for _ in br]
+    extra = rng.standard_normal((T, W))
+    for n in (1, 2, 3):
+        xs = _dev(x, torch.float32)
+        ops.norm_mean_add(xs, [_dev(b, torch.float32) for b in br[:n]], [_dev(w, torch.float32) for w in ws[:n]], 1e-6, 0.3 / n,
+                          _dev(extra, torch.float32), 0.3)
+        want = x + 0.3 * (sum(P.rms_norm(b, w, 1e-6) for b, w in zip(br[:n], ws[:n])) / n + extra)
+        assert np.abs(xs.cpu().numpy() - want).max() <= 1e-5 * np.abs(want).max()
+    z = rng.standard_normal((T, W)) * 3
+    z_r = z if dtype == "float32" else _bf16_round(z)
+    for kind, fn in (("relu2", P.relu_squared), ("gelu_tanh", P.gelu_tanh), ("silu", P.silu)):
+        t = _dev(z_r, tdt)
+        ops.activation(t, t, kind)
+        assert np.abs(t.float().cpu().numpy() - fn(z_r)).max() <= tol * np.abs(fn(z_r)).max()
+    lg = _dev(z * 20, torch.float32)
+    ops.softcap(lg, 30.0)
+    assert np.abs(lg.cpu().numpy() - P.soft_cap((z * 20).astype(np.float32), 30.0)).max() <= 1e-4
+    table = rng.standard_normal((11, W))
+    table_r = table if dtype == "float32" else _bf16_round(table)
+    ids = rng.integers(0, 11, T).astype(np.int32)
+    vec = rng.standard_normal(W)
+    status = ops.new_status("cuda")
+    xs = _dev(x, torch.float32)
+    ops.stream_inject(xs, _dev(table_r, tdt), _dev(ids), _dev(vec, torch.float32), status)
+    assert np.abs(xs.cpu().numpy() - (x + table_r[ids] + vec)).max() <= 1e-5
+    xs = _dev(x, torch.float32)
+    ops.stream_inject(xs, None, None, _dev(vec, torch.float32), status)
+    assert np.abs(xs.cpu().numpy() - (x + vec)).max() <= 1e-5
+    ops.read_status(status)
+
+
+# ---- keys made to stand out ---------------------------------------------------------------------------------------
+
+def _crafted_model(tmp, window, page_borders_dim=16):
+    """One layer whose left mixer sees one marked token: the embedding row of token 1 has a large component that the
+    query and key projections pass on, so the score of a query against that key dominates the softmax; its value
+    carries a signature that the head makes visible in the logits.  Everything else is small."""
+    from imparo_b200.weights.safetensors_io import write_safetensors
+    import torch
+    cfg = {"architecture": "Vipotar", "vocab": 32, "width": 16, "norm": {"eps": 1e-6}, "residual_mult": 1.0,
+           "layers": [{"type": "parallel", "mlp": None, "mixer": {
+               "left": {"heads": 2, "kv_heads": 1, "dim": 16, "vdim": 16, "scale": 1.0, "mask": {"size": window}},
+               "right": {"heads": 1, "dim": 4, "vdim": 4, "decay": [0.0]}}}]}
+    rng = np.random.default_rng(0)
+    t = {}
+    emb = rng.standard_normal((32, 16)) * 0.05
+    emb[1] = 0.0
+    emb[1, 0] = 4.0                     # the marked token
+    emb[2:, 1] = 1.0                    # all others share a direction the queries use
+    t["embed"] = emb
+    t["l0.norm1"] = np.ones(16)
+    q = np.zeros((32, 16)); k = np.zeros((16, 16)); v = np.zeros((16, 16))
+    q[0, 1] = 6.0; q[16, 1] = 6.0       # both heads: query component 0 from the shared direction
+    k[0, 0] = 6.0                       # key component 0 from the marked direction
+    v[:, :] = np.eye(16)
+    t["l0.mix.left.q"], t["l0.mix.left.k"], t["l0.mix.left.v"] = q, k, v
+    t["l0.mix.left.o"] = np.concatenate([np.eye(16), np.zeros((16, 16))], axis=1)
+    for n, s in (("q", (4, 16)), ("k", (4, 16)), ("v", (4, 16)), ("g", (4, 16)), ("o", (16, 4))):
+        t["l0.mix.right." + n] = rng.standard_normal(s) * 0.01
+    t["l0.mix.right.norm"] = np.ones(4)
+    t["l0.mix.left.out"] = np.ones(16)
+    t["l0.mix.right.out"] = np.ones(16) * 0.01
+    t["final.norm"] = np.ones(16)
+    t["head"] = rng.standard_normal((32, 16))
+    os.makedirs(tmp, exist_ok=True)
+    with open(os.path.join(tmp, "config.json"), "w") as f:
+        json.dump(cfg, f)
+    tensors = {n: torch.as_tensor(a, dtype=torch.float32).to(torch.float32 if n.endswith(("norm1", ".norm", ".out", "final.norm")) else torch.bfloat16)
+               for n, a in t.items()}
+    write_safetensors(os.path.join(tmp, "model.safetensors"), tensors, {})
+    return cfg
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("window,page,mark", [(9, 4, 7), (16, 16, 15), (17, 8, 0), (5, 16, 30), (64, 16, 3)])
+def test_a_marked_key_just_inside_and_just_outside_the_window(tmp_path, dtype, window, page, mark):
+    """The marked token stands at `mark`; the logits at mark + window - 1 (it is the oldest key still seen) and at
+    mark + window (it has just left) differ strongly in the plain implementation, and the engine gives both, in a
+    prompt's portion and decoded one by one, with the marked key at, before and after page borders."""
+    from imparo_b200.engine import Engine, StepItem
+    cfg = _crafted_model(str(tmp_path / "m"), window)
+    w = read_safetensors(str(tmp_path / "m" / "model.safetensors"))
+    rng = np.random.default_rng(mark)
+    T = mark + window + 6
+    toks = rng.integers(2, 32, T).tolist()
+    toks[mark] = 1
+    ref = P.forward(cfg, w, toks)
+    inside, outside = mark + window - 1, mark + window
+    scale = float(np.abs(ref).max())
+    assert np.abs(ref[inside] - ref[outside]).max() > 0.2 * scale          # the test's weights do show the edge
+    tol = TOL[dtype] * scale
+    for cut in (T, mark + 1, inside, outside):                            # whole; then the edge reached by decoding
+        eng = Engine(str(tmp_path / "m"), dtype=dtype, ctx=128, parallel=2, page_size=page, num_pages=-(-128 // page))
+        eng.add_request(1)
+        got = [eng.step([StepItem(1, toks[:cut], list(range(cut)))]).cpu().numpy()]
+        for i in range(cut, T):
+            got.append(eng.step([StepItem(1, [toks[i]], [0])]).cpu().numpy())
+        got = np.concatenate(got)
+        eng.check_device_status()
+        err = np.abs(got - ref).max(axis=1)
+        assert err.max() <= tol, (cut, int(err.argmax()), float(err.max()), tol)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_a_far_token_is_carried_by_the_state(dtype):
+    """Configuration C has no window on its first layer and a decay of 0.999 there: changing token 0 of a 300-token
+    prompt changes the last logits in the plain implementation, and the engine follows both variants, whole and with
+    the prompt cut into portions and single tokens."""
+    name = "C"
+    base = make_requests(name, [300], seed=40)["r0"]
+    other = list(base)
+    other[0] = (base[0] + 1) % ALL[name]["vocab"]
+    reqs = {"a": base, "b": other}
+    ref = plain_logits(name, reqs)
+    scale = float(np.abs(ref["a"]).max())
+    assert np.abs(ref["a"][-1] - ref["b"][-1]).max() > 100 * TOL[dtype] * scale or dtype == "bfloat16"
+    for build in (traces.whole, lambda r: traces.portions(r, sizes=(64, 2, 33, 1, 1, 100)), lambda r: traces.tail_one_by_one(r, tail=40)):
+        steps = build(reqs)
+        check_trace(engine_for(name, dtype, steps), steps, name, reqs, dtype)
+
+
+# ---- generation through the framework's entry points ----------------------------------------------------------------
+
+def plain_generate(name, prompt, n_new):
+    toks, out, margins = list(prompt), [], []
+    for _ in range(n_new):
+        row = plain_logits(name, {"g": toks})["g"][-1]
+        t = int(np.argmax(row))
+        top2 = np.partition(row, -2)[-2:]
+        out.append(t)
+        margins.append(float(top2[1] - top2[0]))
+        toks.append(t)
+    return out, margins
+
+
+@pytest.mark.parametrize("dtype,min_margin", [("float32", 1e-4), ("bfloat16", 0.15)])
+@pytest.mark.parametrize("name", ["A", "B", "E"])
+def test_greedy_generation_through_the_scheduler(name, dtype, min_margin):
+    """Three prompts through Engine.generate: continuous batching with prompt portions of at most 8 tokens beside
+    decoding requests, two state slots for three requests, pages used again."""
+    from imparo_b200.engine import Engine
+    from tests.test_generate_gpu import agree
+    prompts = list(make_requests(name, [5, 23, 40], seed=1).values())
+    page = PAGE[name]
+    eng = Engine(model_dir(name), dtype=dtype, ctx=64, parallel=2, page_size=page, num_pages=2 * (64 // page), max_step_tokens=8)
+    got = eng.generate(prompts, max_tokens=10)
+    for i, p in enumerate(prompts):
+        want, margins = plain_generate(name, p, 10)
+        agree(got[i], want, margins, min_margin)
+    assert eng.cache.n_requests() == 0
+    eng.cache.check()
+
+
+def test_command_line_and_trace_runner(tmp_path):
+    from tests.test_trace_run_gpu import replay
+    name = "A"
+    prompt = make_requests(name, [16], seed=0)["r0"]
+    want, _ = plain_generate(name, prompt, 6)
+    tf = tmp_path / "tokens.txt"
+    tf.write_text(" ".join(map(str, prompt)))
+    r = subprocess.run([sys.executable, "-m", "imparo_b200", "-m", model_dir(name), "--dtype", "float32", "--decode", "6",
+                        "-c", "64", "-t", str(tf), "--json"], cwd=ROOT, capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stderr[-2000:]
+    assert json.loads(r.stdout.strip().splitlines()[-1])["tokens"] == [want]
+    reqs = make_requests(name, [70, 33, 90, 41, 64, 52], seed=7)
+    steps = traces.mixed(reqs, seed=1)
+    max_tokens = traces.max_live_tokens(steps, 64)
+    out = tmp_path / "out"
+    replay(model_dir(name), "bfloat16", steps, out, max_tokens)
+    ref = plain_logits(name, reqs)
+    want = traces.expected(steps, ref)
+    got = {s["step"]: np.fromfile(out / f"{s['step']}.f32", dtype="<f4").reshape(-1, ALL[name]["vocab"]) for s in steps if s["step"] in want}
+    scale = max(float(np.abs(v).max()) for v in ref.values())
+    errs = all_errors(steps, got, want)
+    assert max(e[3] for e in errs) <= WORST["bfloat16"] * scale
+    assert sum(e[3] > TOL["bfloat16"] * scale for e in errs) <= 0.1 * len(errs)
