@@ -20,7 +20,9 @@ captured for its shape, as every step whose shape repeats is.
 --workload continuous | long run the baseline's two other workloads (LFM2-700M sizes under
 continuous batching; LFM2-350M sizes with 32,768-token prompts in bfloat16 and 32-bit) and
 print one JSON line each; --workload sizes runs the headline's model at further prompt lengths
-and decode contexts; the default is the headline above.
+and decode contexts; --workload vipotar runs the Vipotar design at two sizes that resemble a real model's layers beside
+LFM2 at equal width, depth, heads and feed-forward size (prefill of one prompt, decode at batch 8); the default is the
+headline above.
 """
 import argparse
 import json
@@ -233,6 +235,99 @@ def workload_sizes(args):
                                                            "frac": round(nbytes / (ms * 1e-3) / 1e9 / pk["hbm_gbs"], 4)}}
     out["peaks"] = pk["source"]
     out["config"] = {"model": "LFM2-1.2B", "layers": 16, "layers_of_config": 16, "page_size": PAGE, "params": n_params}
+    out["clocks"] = clocks.summary()
+    print(json.dumps(out))
+    return 0
+
+
+def vipotar_config(width, layers, heads, kv_heads, head, window, lin_heads, lin_dim, lin_vdim, ff, vocab):
+    """A Vipotar config.json of the given sizes: every layer the same, no repeated stretch, half of each head rotated
+    with scaled frequencies, decays spread between 0.9 and 0.999."""
+    left = {"heads": heads, "kv_heads": kv_heads, "dim": head, "vdim": head, "scale": head ** -0.5, "mask": {"size": window},
+            "rot": {"dims": head // 2, "base": 500000.0, "scaling": {"factor": 4.0, "original": 2048, "fast": 32.0, "slow": 1.0}}}
+    decay = [1.0 - 0.1 * (0.01 ** (h / max(lin_heads - 1, 1))) for h in range(lin_heads)]
+    right = {"heads": lin_heads, "dim": lin_dim, "vdim": lin_vdim, "decay": decay}
+    layer = {"type": "parallel", "mixer": {"left": left, "right": right}, "mlp": {"kind": "dense", "ff": ff}}
+    return {"architecture": "Vipotar", "vocab": vocab, "width": width, "norm": {"eps": 1e-6}, "residual_mult": 0.5,
+            "logit_softcap": 30.0, "layers": [layer] * layers}
+
+
+def lfm2_like(width, layers, heads, kv_heads, head, ff, vocab):
+    """LFM2 at the same width, depth, heads and feed-forward size: two layers in three are short convolutions."""
+    types = ["full_attention" if i % 3 == 2 else "conv" for i in range(layers)]
+    return {"architectures": ["Lfm2ForCausalLM"], "model_type": "lfm2", "vocab_size": vocab, "hidden_size": width,
+            "num_hidden_layers": layers, "layer_types": types, "num_attention_heads": heads, "num_key_value_heads": kv_heads,
+            "head_dim": head, "block_ff_dim": ff, "block_auto_adjust_ff_dim": False, "conv_L_cache": 3, "conv_bias": False,
+            "rope_theta": 1000000.0, "norm_eps": 1e-5, "tie_embedding": True, "max_position_embeddings": 128000}
+
+
+def workload_vipotar(args):
+    """Vipotar at two sizes beside LFM2 at equal sizes: prefill of one prompt of 512 and 2,048 tokens, decode steps of 8
+    requests with 2,048 positions each.  Rooflines: prefill against the measured bfloat16 peak with the flops the design
+    needs (products over all tokens, attention over the window, the linear attention's 4 * heads * dim * vdim per token);
+    decode against the measured copy bandwidth with the bytes a step must move (every matrix once, the windows' keys and
+    values, the linear attention's states read and written)."""
+    import numpy as np
+    import torch
+    from imparo_b200.engine import Engine
+    rng = np.random.default_rng(0)
+    pk = peaks()
+    sizes = {"width1024": dict(width=1024, layers=8, heads=16, kv_heads=4, head=64, window=512, lin_heads=8, lin_dim=64, lin_vdim=128,
+                               ff=4096, vocab=32768),
+             "width2048": dict(width=2048, layers=8, heads=32, kv_heads=8, head=64, window=1024, lin_heads=16, lin_dim=128, lin_vdim=128,
+                               ff=8192, vocab=65536)}
+    out = {"metric": "Vipotar beside LFM2 at equal sizes: prefill of one prompt, decode at batch 8 with 2,048 positions",
+           "unit": "tokens/s", "dtype": "bf16", "data": "synthetic (random weights, uniform-random token ids)", "sizes": {}}
+    with ClockSampler() as clocks:
+        for name, z in sizes.items():
+            row = {}
+            W, L, F, V = z["width"], z["layers"], z["ff"], z["vocab"]
+            for model in ("vipotar", "lfm2"):
+                if model == "vipotar":
+                    cfg = vipotar_config(**z)
+                    qkv = (z["heads"] + 2 * z["kv_heads"]) * z["head"] * W + W * z["heads"] * z["head"]
+                    lin = (2 * z["lin_heads"] * z["lin_dim"] + 2 * z["lin_heads"] * z["lin_vdim"]) * W + W * z["lin_heads"] * z["lin_vdim"]
+                    matrix = L * (qkv + lin + 2 * W * F)
+                    state = L * z["lin_heads"] * z["lin_dim"] * z["lin_vdim"] * 4
+                    kv_tok = L * 2 * z["kv_heads"] * z["head"] * 2
+                    head_params = V * W
+
+                    def flops(T):
+                        keys = sum(min(t + 1, z["window"]) for t in range(T))
+                        return 2.0 * T * matrix + 2.0 * V * W + L * (4.0 * z["heads"] * z["head"] * keys
+                                                                     + 4.0 * z["lin_heads"] * z["lin_dim"] * z["lin_vdim"] * T)
+
+                    def step_bytes(batch, ctx):
+                        return (matrix + head_params) * 2 + batch * (2 * state + min(ctx, z["window"]) * kv_tok)
+                else:
+                    cfg = lfm2_like(W, L, z["heads"], z["kv_heads"], z["head"], F, V)
+                    n_attn = sum(1 for t in cfg["layer_types"] if t != "conv")
+                    attn = (z["heads"] + 2 * z["kv_heads"]) * z["head"] * W + W * z["heads"] * z["head"]
+                    matrix = L * 3 * W * F + (L - n_attn) * 4 * W * W + n_attn * attn
+                    kv_tok = n_attn * 2 * z["kv_heads"] * z["head"] * 2
+
+                    def flops(T):
+                        return 2.0 * T * matrix + 2.0 * V * W + n_attn * 4.0 * z["heads"] * z["head"] * T * (T + 1) / 2
+
+                    def step_bytes(batch, ctx):
+                        return (matrix + V * W) * 2 + batch * ctx * kv_tok
+                engine = Engine(config=cfg, seed=0, dtype="bfloat16", ctx=CTX, parallel=8, page_size=PAGE, max_step_tokens=PROMPT,
+                                random_init={"norm_jitter": 0.0})
+                r = {"params": matrix + V * W * (2 if model == "vipotar" else 1), "prefill": {}}
+                for T in (512, 2048):
+                    ms = measure_prefill(engine, reps=5, warmup=3, rng=rng, prompt=T)
+                    r["prefill"][str(T)] = {"value": round(T * 1000.0 / ms, 1), "ms": round(ms, 3),
+                                            "frac": round(flops(T) / (ms * 1e-3) / (pk["bf16_tflops_burst"] * 1e12), 4)}
+                ms, launches, library, ctx = measure_decode(engine, 8, max(20, args.steps // 4), max(args.warmup, 3), rng, prompt=PROMPT)
+                nbytes = step_bytes(8, ctx)
+                r["decode_b8"] = {"value": round(8 * 1000.0 / ms, 1), "ms_per_step": round(ms, 4), "own_kernels_per_step": round(launches, 1),
+                                  "library_gemms_per_step": round(library, 1), "bytes_per_step": int(nbytes),
+                                  "frac": round(nbytes / (ms * 1e-3) / 1e9 / pk["hbm_gbs"], 4)}
+                row[model] = r
+                del engine
+                torch.cuda.empty_cache()
+            out["sizes"][name] = dict(row, config=z)
+    out["peaks"] = pk["source"]
     out["clocks"] = clocks.summary()
     print(json.dumps(out))
     return 0
@@ -456,10 +551,11 @@ def main():
     ap.add_argument("--skip-points", action="store_true", help="skip the batch-1 and batch-64 points")
     ap.add_argument("--only-decode", action="store_true", help="time the decode steps only (for profiler captures)")
     ap.add_argument("--only-prefill", action="store_true", help="time the 2,048-token prompt only (for profiler captures)")
-    ap.add_argument("--workload", default="headline", choices=["headline", "continuous", "long", "sizes"],
+    ap.add_argument("--workload", default="headline", choices=["headline", "continuous", "long", "sizes", "vipotar"],
                     help="headline (default): the line the contract names.  continuous: LFM2-700M sizes, requests with prompts "
                          "of 64 to 4,096 tokens through 32 slots in 512-token portions beside decode rows, temperature 0.7, 128 new "
-                         "tokens each.  long: LFM2-350M sizes, 4 prompts of 32,768 tokens and 512 greedy tokens each, bfloat16 and 32-bit")
+                         "tokens each.  long: LFM2-350M sizes, 4 prompts of 32,768 tokens and 512 greedy tokens each, bfloat16 and 32-bit.  "
+                         "vipotar: the Vipotar design at two sizes beside LFM2 at equal sizes")
     ap.add_argument("--requests", type=int, default=32, help="continuous: requests in all (the baseline's workload has 32)")
     ap.add_argument("--long-check-layers", type=int, default=4, help="long: layers of the 32-bit check against the plain implementation")
     args = ap.parse_args()
@@ -481,6 +577,8 @@ def main():
         return workload_long(args)
     if args.workload == "sizes":
         return workload_sizes(args)
+    if args.workload == "vipotar":
+        return workload_vipotar(args)
     cfg = dict(LFM2_1_2B)
     if args.layers is not None and args.layers < cfg["num_hidden_layers"]:
         cfg["layer_types"] = cfg["layer_types"][:args.layers]

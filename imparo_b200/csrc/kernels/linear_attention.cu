@@ -12,6 +12,7 @@
 // then each row costs dim multiply-adds for the state and dim for the output.  Everything that enters the
 // recurrence is 32-bit; only the projections are read in the activations' dtype.
 #include "common.cuh"
+#include <mma.h>
 
 namespace imparo {
 
@@ -169,16 +170,228 @@ linear_attention_scan_kernel(const float* __restrict__ decay, float* __restrict_
     float* sp = state + ((size_t)slot * heads + h) * per_head + e;
     float s = *sp;
     const float dec_full = powf(dec, (float)chunk);
-    int c = first;
-    for (int r = r0; r < r1; r += chunk, ++c) {
-        const int n = min(chunk, r1 - r);
-        float* cp = chunk_state + ((size_t)c * heads + h) * per_head + e;
-        const float local = *cp;
-        *cp = s;
-        s = (n == chunk ? dec_full : powf(dec, (float)n)) * s + local;
+    const int nc = (r1 - r0 + chunk - 1) / chunk;
+    const size_t cstride = (size_t)heads * per_head;
+    float* cp = chunk_state + ((size_t)first * heads + h) * per_head + e;
+    for (int c0 = 0; c0 < nc; c0 += 8) {                      // eight chunks' sums requested together, then the chain
+        float loc[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) loc[u] = c0 + u < nc ? __ldcg(cp + (size_t)(c0 + u) * cstride) : 0.f;
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+            if (c0 + u < nc) {
+                const int n = min(chunk, r1 - r0 - (c0 + u) * chunk);
+                cp[(size_t)(c0 + u) * cstride] = s;
+                s = (n == chunk ? dec_full : powf(dec, (float)n)) * s + loc[u];
+            }
+        }
     }
     *sp = s;
 }
+
+
+// ---- the chunks on tensor cores (bfloat16, key and value sizes multiples of 16 up to 128, chunks of 64 rows) ----
+// With Q, K [64, dim] and V [64, vdim] the chunk's activated rows (bfloat16) and d the head's decay:
+//   local:  L = sum_j d^(n-1-j) k_j v_j^T = Kd^T V, Kd_j = d^(n-1-j) k_j formed in 32-bit and fed to the tensor cores as the
+//           sum of two bfloat16 numbers (a high and a low part: two products), so that the decays are not rounded to 8 bits
+//   out:    o_i = sum_(j<=i) (q_i.k_j) d^(i-j) v_j + d^(i+1) (S0^T q_i):  scores Q K^T accumulated in 32-bit, multiplied by the
+//           decay powers in 32-bit, rounded to bfloat16 for the product with V (as a softmax's weights are); the state the
+//           chunk starts from enters as a high and a low bfloat16 part (two products) and its rows' decay d^(i+1) multiplies
+//           the 32-bit result.  The state itself is only ever added to in 32-bit (the scan).
+// One CTA of four warps per (chunk, head); wmma fragments of 16 x 16 x 16 (mma.sync); operands staged in padded shared memory.
+namespace lt {
+namespace wm = nvcuda::wmma;
+constexpr int C = 64, PAD = 8, THREADS = 128;
+using bf16 = __nv_bfloat16;
+
+__device__ __forceinline__ bool find_chunk(const int* __restrict__ item_row_start, int n_items, int g, int& r_begin, int& r_end) {
+    int item;
+    return la_find_chunk(item_row_start, n_items, C, g, item, r_begin, r_end);
+}
+
+// rows [r_begin, r_begin + n) x `width` columns at `src` (row stride in elements) -> dst [C][ld] (and lo [C][ld]): activated,
+// times factor(row) in 32-bit, as a bfloat16 high part (and the low part of what that rounding lost); rows from n on are zero
+template <bool SILU, bool SPLIT, typename F>
+__device__ __forceinline__ void stage(const bf16* __restrict__ src, size_t row_stride, int r_begin, int n, int width,
+                                      bf16* __restrict__ dst, bf16* __restrict__ lo, int ld, F factor) {
+    const int vecs = width / 8;
+    for (int idx = threadIdx.x; idx < C * vecs; idx += THREADS) {
+        const int r = idx / vecs, c = (idx - r * vecs) * 8;
+        uint4 hi4 = make_uint4(0u, 0u, 0u, 0u), lo4 = hi4;
+        if (r < n) {
+            const uint4 raw = *reinterpret_cast<const uint4*>(src + (size_t)(r_begin + r) * row_stride + c);
+            const bf16* e = reinterpret_cast<const bf16*>(&raw);
+            const float f = factor(r);
+            bf16* ho = reinterpret_cast<bf16*>(&hi4);
+            bf16* lw = reinterpret_cast<bf16*>(&lo4);
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+                float x = __bfloat162float(e[u]);
+                if (SILU) x = silu(x);
+                x *= f;
+                ho[u] = __float2bfloat16_rn(x);
+                if (SPLIT) lw[u] = __float2bfloat16_rn(x - __bfloat162float(ho[u]));
+            }
+        }
+        *reinterpret_cast<uint4*>(dst + (size_t)r * ld + c) = hi4;
+        if (SPLIT) *reinterpret_cast<uint4*>(lo + (size_t)r * ld + c) = lo4;
+    }
+}
+
+template <bool SILU>
+__global__ void __launch_bounds__(THREADS)
+local_kernel(const bf16* __restrict__ k, const bf16* __restrict__ v, size_t row_stride, const float* __restrict__ decay,
+             float* __restrict__ chunk_state, const int* __restrict__ item_row_start, int n_items, int heads, int dim, int vdim) {
+    extern __shared__ __align__(128) unsigned char lt_smem[];
+    __shared__ float pw[C + 1];
+    pdl_trigger();
+    const int g = blockIdx.x, h = blockIdx.y;
+    int r_begin, r_end;
+    const bool found = find_chunk(item_row_start, n_items, g, r_begin, r_end);
+    const float dec = decay[h];
+    if (threadIdx.x <= C) pw[threadIdx.x] = powf(dec, (float)threadIdx.x);
+    pdl_wait();
+    if (!found) return;
+    const int n = r_end - r_begin;
+    const int ldk = dim + PAD, ldv = vdim + PAD;
+    bf16* k_hi = reinterpret_cast<bf16*>(lt_smem);
+    bf16* k_lo = k_hi + C * ldk;
+    bf16* v_s = k_lo + C * ldk;
+    __syncthreads();
+    stage<SILU, true>(k + (size_t)h * dim, row_stride, r_begin, n, dim, k_hi, k_lo, ldk, [&](int r) { return pw[n - 1 - r]; });
+    stage<SILU, false>(v + (size_t)h * vdim, row_stride, r_begin, n, vdim, v_s, nullptr, ldv, [](int) { return 1.f; });
+    __syncthreads();
+    const int warp = threadIdx.x >> 5;
+    const int dts = dim / 16, vts = vdim / 16;
+    float* dst = chunk_state + ((size_t)g * heads + h) * dim * vdim;
+    const int steps = (n + 15) / 16;                          // rows from n on are zero
+    for (int t = warp; t < dts * vts; t += THREADS / 32) {
+        const int dt = t / vts, vt = t - dt * vts;
+        wm::fragment<wm::accumulator, 16, 16, 16, float> acc;
+        wm::fill_fragment(acc, 0.f);
+        for (int jj = 0; jj < steps; ++jj) {
+            wm::fragment<wm::matrix_a, 16, 16, 16, bf16, wm::col_major> a_hi, a_lo;      // (d, j) at [j * ld + d]
+            wm::fragment<wm::matrix_b, 16, 16, 16, bf16, wm::row_major> b;
+            wm::load_matrix_sync(a_hi, k_hi + (size_t)jj * 16 * ldk + dt * 16, ldk);
+            wm::load_matrix_sync(a_lo, k_lo + (size_t)jj * 16 * ldk + dt * 16, ldk);
+            wm::load_matrix_sync(b, v_s + (size_t)jj * 16 * ldv + vt * 16, ldv);
+            wm::mma_sync(acc, a_hi, b, acc);
+            wm::mma_sync(acc, a_lo, b, acc);
+        }
+        wm::store_matrix_sync(dst + (size_t)dt * 16 * vdim + vt * 16, acc, vdim, wm::mem_row_major);
+    }
+}
+
+template <bool SILU>
+__global__ void __launch_bounds__(THREADS)
+out_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k, const bf16* __restrict__ v, size_t row_stride,
+           const float* __restrict__ decay, const float* __restrict__ chunk_state, const int* __restrict__ item_row_start,
+           int n_items, float* __restrict__ out, int heads, int dim, int vdim) {
+    extern __shared__ __align__(128) unsigned char lt_smem[];
+    __shared__ float pw[C + 1];
+    pdl_trigger();
+    const int g = blockIdx.x, h = blockIdx.y;
+    int r_begin, r_end;
+    const bool found = find_chunk(item_row_start, n_items, g, r_begin, r_end);
+    const float dec = decay[h];
+    if (threadIdx.x <= C) pw[threadIdx.x] = powf(dec, (float)threadIdx.x);
+    pdl_wait();
+    if (!found) return;
+    const int n = r_end - r_begin;
+    const int ldq = dim + PAD, ldv = vdim + PAD, lds = vdim + PAD, ldaf = C + 4, ldab = C + PAD, ldp = 20;
+    bf16* q_s = reinterpret_cast<bf16*>(lt_smem);
+    bf16* k_s = q_s + C * ldq;
+    bf16* v_s = k_s + C * ldq;
+    bf16* s_hi = v_s + C * ldv;
+    bf16* s_lo = s_hi + dim * lds;
+    bf16* a_bf = s_lo + dim * lds;
+    float* a_f = reinterpret_cast<float*>(a_bf + C * ldab);
+    float* patch = a_f + C * ldaf + (threadIdx.x >> 5) * 16 * ldp;
+    auto one = [](int) { return 1.f; };
+    stage<SILU, false>(q + (size_t)h * dim, row_stride, r_begin, n, dim, q_s, nullptr, ldq, one);
+    stage<SILU, false>(k + (size_t)h * dim, row_stride, r_begin, n, dim, k_s, nullptr, ldq, one);
+    stage<SILU, false>(v + (size_t)h * vdim, row_stride, r_begin, n, vdim, v_s, nullptr, ldv, one);
+    {
+        const float* src = chunk_state + ((size_t)g * heads + h) * dim * vdim;
+        const int vecs = vdim / 4;
+        for (int idx = threadIdx.x; idx < dim * vecs; idx += THREADS) {
+            const int r = idx / vecs, c = (idx - r * vecs) * 4;
+            const float4 x = __ldcg(reinterpret_cast<const float4*>(src + (size_t)r * vdim + c));
+            const bf16 h0 = __float2bfloat16_rn(x.x), h1 = __float2bfloat16_rn(x.y), h2 = __float2bfloat16_rn(x.z), h3 = __float2bfloat16_rn(x.w);
+            bf16* ph = s_hi + (size_t)r * lds + c;
+            bf16* pl = s_lo + (size_t)r * lds + c;
+            ph[0] = h0; ph[1] = h1; ph[2] = h2; ph[3] = h3;
+            pl[0] = __float2bfloat16_rn(x.x - __bfloat162float(h0)); pl[1] = __float2bfloat16_rn(x.y - __bfloat162float(h1));
+            pl[2] = __float2bfloat16_rn(x.z - __bfloat162float(h2)); pl[3] = __float2bfloat16_rn(x.w - __bfloat162float(h3));
+        }
+    }
+    __syncthreads();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int kts = dim / 16, vts = vdim / 16;
+    // scores of the tiles on and below the diagonal: (0,0) (1,0) (1,1) (2,0) ... (3,3)
+    for (int t = warp; t < 10; t += THREADS / 32) {
+        int it = 0, jt = t;
+        while (jt > it) { jt -= it + 1; ++it; }
+        wm::fragment<wm::accumulator, 16, 16, 16, float> acc;
+        wm::fill_fragment(acc, 0.f);
+        for (int kk = 0; kk < kts; ++kk) {
+            wm::fragment<wm::matrix_a, 16, 16, 16, bf16, wm::row_major> a;
+            wm::fragment<wm::matrix_b, 16, 16, 16, bf16, wm::col_major> b;               // (d, j) at [j * ld + d]
+            wm::load_matrix_sync(a, q_s + (size_t)it * 16 * ldq + kk * 16, ldq);
+            wm::load_matrix_sync(b, k_s + (size_t)jt * 16 * ldq + kk * 16, ldq);
+            wm::mma_sync(acc, a, b, acc);
+        }
+        wm::store_matrix_sync(a_f + (size_t)it * 16 * ldaf + jt * 16, acc, ldaf, wm::mem_row_major);
+    }
+    __syncthreads();
+    for (int idx = threadIdx.x; idx < C * C; idx += THREADS) {
+        const int i = idx / C, j = idx - i * C;
+        const float w = (j <= i && i < n) ? a_f[(size_t)i * ldaf + j] * pw[i - j] : 0.f;
+        a_bf[(size_t)i * ldab + j] = __float2bfloat16_rn(w);
+    }
+    __syncthreads();
+    for (int t = warp; t < 4 * vts; t += THREADS / 32) {
+        const int it = t & 3, vt = t >> 2;
+        wm::fragment<wm::accumulator, 16, 16, 16, float> acc;
+        wm::fill_fragment(acc, 0.f);
+        for (int kk = 0; kk < kts; ++kk) {                   // the state the chunk starts from: S0^T q, high and low part
+            wm::fragment<wm::matrix_a, 16, 16, 16, bf16, wm::row_major> a;
+            wm::fragment<wm::matrix_b, 16, 16, 16, bf16, wm::row_major> b_hi, b_lo;
+            wm::load_matrix_sync(a, q_s + (size_t)it * 16 * ldq + kk * 16, ldq);
+            wm::load_matrix_sync(b_hi, s_hi + (size_t)kk * 16 * lds + vt * 16, lds);
+            wm::load_matrix_sync(b_lo, s_lo + (size_t)kk * 16 * lds + vt * 16, lds);
+            wm::mma_sync(acc, a, b_hi, acc);
+            wm::mma_sync(acc, a, b_lo, acc);
+        }
+        wm::store_matrix_sync(patch, acc, ldp, wm::mem_row_major);
+        __syncwarp();
+        for (int e = lane; e < 256; e += 32) patch[(e >> 4) * ldp + (e & 15)] *= pw[it * 16 + (e >> 4) + 1];
+        __syncwarp();
+        wm::load_matrix_sync(acc, patch, ldp, wm::mem_row_major);
+        for (int jj = 0; jj <= it; ++jj) {                    // the chunk's own rows up to the diagonal
+            wm::fragment<wm::matrix_a, 16, 16, 16, bf16, wm::row_major> a;
+            wm::fragment<wm::matrix_b, 16, 16, 16, bf16, wm::row_major> b;
+            wm::load_matrix_sync(a, a_bf + (size_t)it * 16 * ldab + jj * 16, ldab);
+            wm::load_matrix_sync(b, v_s + (size_t)jj * 16 * ldv + vt * 16, ldv);
+            wm::mma_sync(acc, a, b, acc);
+        }
+        __syncwarp();
+        wm::store_matrix_sync(patch, acc, ldp, wm::mem_row_major);
+        __syncwarp();
+        for (int e = lane; e < 256; e += 32) {
+            const int r = it * 16 + (e >> 4);
+            if (r < n) out[(size_t)(r_begin + r) * ((size_t)heads * vdim) + (size_t)h * vdim + vt * 16 + (e & 15)] = patch[(e >> 4) * ldp + (e & 15)];
+        }
+        __syncwarp();
+    }
+}
+
+static size_t local_smem(int dim, int vdim) { return (size_t)C * (2 * (dim + PAD) + (vdim + PAD)) * 2; }
+static size_t out_smem(int dim, int vdim) {
+    return (size_t)C * (2 * (dim + PAD) + (vdim + PAD)) * 2 + (size_t)2 * dim * (vdim + PAD) * 2 + (size_t)C * (C + PAD) * 2 +
+           (size_t)C * (C + 4) * 4 + (size_t)(THREADS / 32) * 16 * 20 * 4;
+}
+}  // namespace lt
 
 }  // namespace imparo
 
@@ -217,6 +430,38 @@ extern "C" int imparo_linear_attention_chunked(const void* q, const void* k, con
                                                cudaStream_t stream) {
     if (n_items <= 0) return 0;
     if (dim < 1 || dim > 256 || vdim < 1 || heads < 1 || heads > 65535 || chunk < 1 || max_chunks < 1) return -3;
+    const bool tensor = dtype == IMPARO_DT_BF16 && chunk == lt::C && dim % 16 == 0 && vdim % 16 == 0 && dim <= 128 && vdim <= 128 &&
+                        row_stride % 8 == 0 && (((uintptr_t)q | (uintptr_t)k | (uintptr_t)v) & 15) == 0 && (heads * dim) % 8 == 0;
+    if (tensor) {
+        static bool configured = false;
+        if (!configured) {
+            cudaError_t e = cudaSuccess;
+            const int most_out = (int)lt::out_smem(128, 128), most_local = (int)lt::local_smem(128, 128);
+            if (e == cudaSuccess) e = cudaFuncSetAttribute(lt::local_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, most_local);
+            if (e == cudaSuccess) e = cudaFuncSetAttribute(lt::local_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, most_local);
+            if (e == cudaSuccess) e = cudaFuncSetAttribute(lt::out_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, most_out);
+            if (e == cudaSuccess) e = cudaFuncSetAttribute(lt::out_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, most_out);
+            if (e != cudaSuccess) return (int)e;
+            configured = true;
+        }
+        const lt::bf16 *qb = (const lt::bf16*)q, *kb = (const lt::bf16*)k, *vb = (const lt::bf16*)v;
+        dim3 tgrid(max_chunks, heads);
+        if (act_silu) launch(lt::local_kernel<true>, tgrid, dim3(lt::THREADS), lt::local_smem(dim, vdim), stream, kb, vb, (size_t)row_stride,
+                             decay, chunk_state, item_row_start, n_items, heads, dim, vdim);
+        else launch(lt::local_kernel<false>, tgrid, dim3(lt::THREADS), lt::local_smem(dim, vdim), stream, kb, vb, (size_t)row_stride,
+                    decay, chunk_state, item_row_start, n_items, heads, dim, vdim);
+        IMPARO_CHECK_LAUNCH();
+        const int per_head_t = dim * vdim;
+        launch(linear_attention_scan_kernel, dim3(n_items, heads, (per_head_t + 255) / 256), dim3(256), 0, stream, decay, chunk_state, state,
+               item_row_start, item_slot, n_items, n_slots, chunk, heads, per_head_t, status);
+        IMPARO_CHECK_LAUNCH();
+        if (act_silu) launch(lt::out_kernel<true>, tgrid, dim3(lt::THREADS), lt::out_smem(dim, vdim), stream, qb, kb, vb, (size_t)row_stride,
+                             decay, (const float*)chunk_state, item_row_start, n_items, out, heads, dim, vdim);
+        else launch(lt::out_kernel<false>, tgrid, dim3(lt::THREADS), lt::out_smem(dim, vdim), stream, qb, kb, vb, (size_t)row_stride,
+                    decay, (const float*)chunk_state, item_row_start, n_items, out, heads, dim, vdim);
+        IMPARO_CHECK_LAUNCH();
+        return 0;
+    }
     dim3 grid(max_chunks, heads, (vdim + 31) / 32);
 #define IMPARO_LC4(T_, D_, S_, O_) launch(linear_attention_chunk_kernel<T_, D_, S_, O_>, grid, dim3(32), 0, stream, (const T_*)q, \
         (const T_*)k, (const T_*)v, (size_t)row_stride, decay, chunk_state, item_row_start, n_items, chunk, out, heads, dim, vdim)

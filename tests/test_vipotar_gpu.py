@@ -290,7 +290,7 @@ def test_decayed_linear_attention_kernel(dtype, heads, dim, vdim, decay):
     from imparo_b200.kernels import ops
     tdt = torch.float32 if dtype == "float32" else torch.bfloat16
     rng = np.random.default_rng(dim * 7 + vdim)
-    lens = [37, 5, 64]
+    lens = [37, 5, 64 + 75]
     qk, vv = heads * dim, heads * vdim
     rows = [rng.standard_normal((n, 2 * qk + vv + 3)) * 0.7 for n in lens]          # three columns the kernel must skip
     if dtype == "bfloat16":
@@ -311,7 +311,7 @@ def test_decayed_linear_attention_kernel(dtype, heads, dim, vdim, decay):
     dec = torch.tensor(decay, dtype=torch.float32, device="cuda")
     got = [np.zeros_like(w) for w in want]
     at = [0, 0, 0]
-    for cut in ([20, 2, 31], [16, 1, 2], [1, 1, 1], [0, 1, 30]):
+    for cut in ([20, 2, 31], [16, 1, 2], [1, 1, 1], [0, 1, 30 + 75]):
         items = [i for i in range(3) if cut[i]]
         x = np.concatenate([rows[i][at[i]:at[i] + cut[i]] for i in items])
         starts = np.concatenate([[0], np.cumsum([cut[i] for i in items])]).astype(np.int32)
@@ -330,11 +330,15 @@ def test_decayed_linear_attention_kernel(dtype, heads, dim, vdim, decay):
     # the same rows in chunks that run side by side (chunks of 8 and of 16 rows; the requests' lengths are no multiples),
     # first portions from fresh states, then the rest from the states those left
     final = state[slots].cpu().numpy()
-    for chunk in (8, 16):
+    for chunk in (8, 16, 64):
+        # chunks of 64 rows in bfloat16 with sizes that are multiples of 16 run on the tensor cores: the scores of a chunk are
+        # rounded to bfloat16 for the product with the values, as a softmax's weights are
+        tensor = chunk == 64 and dtype == "bfloat16" and dim % 16 == 0 and vdim % 16 == 0 and dim <= 128 and vdim <= 128
+        tol = 2e-2 if tensor else 1e-5
         state[slots] = 0.0
         got2 = [np.zeros_like(w) for w in want]
         at = [0, 0, 0]
-        for cut in ([30, 3, 41], [7, 2, 23]):
+        for cut in ([30, 3, 41 + 70], [7, 2, 23 + 5]):
             x = np.concatenate([rows[i][at[i]:at[i] + cut[i]] for i in range(3)])
             starts = np.concatenate([[0], np.cumsum(cut)]).astype(np.int32)
             out = torch.empty(len(x), vv, device="cuda")
@@ -348,8 +352,8 @@ def test_decayed_linear_attention_kernel(dtype, heads, dim, vdim, decay):
         ops.read_status(status)
         assert at == lens
         for g, w in zip(got2, want):
-            assert np.abs(g - w).max() <= 1e-5 * max(np.abs(w).max(), 1.0)
-        assert np.abs(state[slots].cpu().numpy() - final).max() <= 1e-5 * max(np.abs(final).max(), 1.0)
+            assert np.abs(g - w).max() <= tol * max(np.abs(w).max(), 1.0)
+        assert np.abs(state[slots].cpu().numpy() - final).max() <= (1e-4 if tensor else 1e-5) * max(np.abs(final).max(), 1.0)
         assert float(state[1].min()) == 7.0 and float(state[5].max()) == 7.0
 
 
