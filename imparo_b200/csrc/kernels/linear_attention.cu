@@ -201,7 +201,7 @@ linear_attention_scan_kernel(const float* __restrict__ decay, float* __restrict_
 // One CTA of four warps per (chunk, head); wmma fragments of 16 x 16 x 16 (mma.sync); operands staged in padded shared memory.
 namespace lt {
 namespace wm = nvcuda::wmma;
-constexpr int C = 64, PAD = 8, THREADS = 128;
+constexpr int C = 64, PAD = 8, THREADS = 256;
 using bf16 = __nv_bfloat16;
 
 __device__ __forceinline__ bool find_chunk(const int* __restrict__ item_row_start, int n_items, int g, int& r_begin, int& r_end) {
@@ -317,12 +317,11 @@ out_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k, const bf16* _
         for (int idx = threadIdx.x; idx < dim * vecs; idx += THREADS) {
             const int r = idx / vecs, c = (idx - r * vecs) * 4;
             const float4 x = __ldcg(reinterpret_cast<const float4*>(src + (size_t)r * vdim + c));
-            const bf16 h0 = __float2bfloat16_rn(x.x), h1 = __float2bfloat16_rn(x.y), h2 = __float2bfloat16_rn(x.z), h3 = __float2bfloat16_rn(x.w);
-            bf16* ph = s_hi + (size_t)r * lds + c;
-            bf16* pl = s_lo + (size_t)r * lds + c;
-            ph[0] = h0; ph[1] = h1; ph[2] = h2; ph[3] = h3;
-            pl[0] = __float2bfloat16_rn(x.x - __bfloat162float(h0)); pl[1] = __float2bfloat16_rn(x.y - __bfloat162float(h1));
-            pl[2] = __float2bfloat16_rn(x.z - __bfloat162float(h2)); pl[3] = __float2bfloat16_rn(x.w - __bfloat162float(h3));
+            const __nv_bfloat162 h01 = __floats2bfloat162_rn(x.x, x.y), h23 = __floats2bfloat162_rn(x.z, x.w);
+            const float2 f01 = __bfloat1622float2(h01), f23 = __bfloat1622float2(h23);
+            const __nv_bfloat162 l01 = __floats2bfloat162_rn(x.x - f01.x, x.y - f01.y), l23 = __floats2bfloat162_rn(x.z - f23.x, x.w - f23.y);
+            *reinterpret_cast<uint2*>(s_hi + (size_t)r * lds + c) = make_uint2(*reinterpret_cast<const uint32_t*>(&h01), *reinterpret_cast<const uint32_t*>(&h23));
+            *reinterpret_cast<uint2*>(s_lo + (size_t)r * lds + c) = make_uint2(*reinterpret_cast<const uint32_t*>(&l01), *reinterpret_cast<const uint32_t*>(&l23));
         }
     }
     __syncthreads();

@@ -29,10 +29,25 @@ __global__ void act_rows_kernel(const T* x, T* out, size_t n, int kind) {
         out[i] = from_f32<T>(act_apply(to_f32(x[i]), kind));
 }
 
+// the same 16 bytes at a time (n a multiple of the vector, both pointers 16-byte aligned)
+template <typename T>
+__global__ void act_rows_vec_kernel(const T* x, T* out, size_t n_vec, int kind) {
+    constexpr int N = 16 / sizeof(T);
+    pdl_trigger();
+    pdl_wait();
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n_vec; i += (size_t)gridDim.x * blockDim.x) {
+        uint4 raw = reinterpret_cast<const uint4*>(x)[i];
+        T* e = reinterpret_cast<T*>(&raw);
+#pragma unroll
+        for (int u = 0; u < N; ++u) e[u] = from_f32<T>(act_apply(to_f32(e[u]), kind));
+        reinterpret_cast<uint4*>(out)[i] = raw;
+    }
+}
+
 // out[r, :] = o[r, :] / rms(o[r, :]) * w * sigmoid(gate[r, :]);  o is 32-bit, gate rows have their own stride
 template <typename T>
 __global__ void gated_rmsnorm_kernel(const float* __restrict__ o, const float* __restrict__ w, float eps,
-                                     const T* __restrict__ gate, size_t gate_stride, T* __restrict__ out, int width) {
+                                     const T* __restrict__ gate, size_t gate_stride, T* __restrict__ out, int width, int vec) {
     __shared__ float scratch[33];
     pdl_trigger();
     pdl_wait();
@@ -40,6 +55,25 @@ __global__ void gated_rmsnorm_kernel(const float* __restrict__ o, const float* _
     const float* orow = o + (size_t)r * width;
     const T* g = gate + (size_t)r * gate_stride;
     float ss = 0.f;
+    if (vec) {                                     // width a multiple of 4, rows 16-byte aligned (8-byte for the gate and out in bfloat16)
+        for (int i = threadIdx.x * 4; i < width; i += blockDim.x * 4) {
+            const float4 v = *reinterpret_cast<const float4*>(orow + i);
+            ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+        }
+        ss = block_sum(ss, scratch);
+        const float scale = 1.0f / sqrtf(ss / (float)width + eps);
+        for (int i = threadIdx.x * 4; i < width; i += blockDim.x * 4) {
+            const float4 v = *reinterpret_cast<const float4*>(orow + i);
+            const float4 ww = *reinterpret_cast<const float4*>(w + i);
+            float gv[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) gv[u] = 1.0f / (1.0f + expf(-to_f32(g[i + u])));
+            T* dst = out + (size_t)r * width + i;
+            dst[0] = from_f32<T>(v.x * scale * ww.x * gv[0]); dst[1] = from_f32<T>(v.y * scale * ww.y * gv[1]);
+            dst[2] = from_f32<T>(v.z * scale * ww.z * gv[2]); dst[3] = from_f32<T>(v.w * scale * ww.w * gv[3]);
+        }
+        return;
+    }
     for (int i = threadIdx.x; i < width; i += blockDim.x) { const float v = orow[i]; ss += v * v; }
     ss = block_sum(ss, scratch);
     const float scale = 1.0f / sqrtf(ss / (float)width + eps);
@@ -56,24 +90,58 @@ struct Branches {
 };
 
 __global__ void norm_mean_add_kernel(float* __restrict__ x, Branches br, int n_branches, float eps, float coef,
-                                     const float* __restrict__ extra, float extra_coef, int width) {
+                                     const float* __restrict__ extra, float extra_coef, int width, int vec) {
     __shared__ float scratch[33];
     pdl_trigger();
     pdl_wait();
     const int r = blockIdx.x;
-    float scale[4];
+    float scale[4] = {0.f, 0.f, 0.f, 0.f};
+    float* xr = x + (size_t)r * width;
+    if (vec) {                                     // width a multiple of 4 and every row 16-byte aligned
+        float ss[4] = {0.f, 0.f, 0.f, 0.f};
+        for (int i = threadIdx.x * 4; i < width; i += blockDim.x * 4) {
+#pragma unroll
+            for (int b = 0; b < 4; ++b) {
+                if (b < n_branches) {
+                    const float4 v = *reinterpret_cast<const float4*>(br.b[b] + (size_t)r * width + i);
+                    ss[b] += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+                }
+            }
+        }
+#pragma unroll
+        for (int b = 0; b < 4; ++b)
+            if (b < n_branches) scale[b] = coef / sqrtf(block_sum(ss[b], scratch) / (float)width + eps);
+        for (int i = threadIdx.x * 4; i < width; i += blockDim.x * 4) {
+            float4 acc = *reinterpret_cast<const float4*>(xr + i);
+            if (extra) {
+                const float4 e = *reinterpret_cast<const float4*>(extra + (size_t)r * width + i);
+                acc.x += extra_coef * e.x; acc.y += extra_coef * e.y; acc.z += extra_coef * e.z; acc.w += extra_coef * e.w;
+            }
+            float4 s = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+            for (int b = 0; b < 4; ++b) {
+                if (b < n_branches) {
+                    const float4 v = *reinterpret_cast<const float4*>(br.b[b] + (size_t)r * width + i);
+                    const float4 ww = *reinterpret_cast<const float4*>(br.w[b] + i);
+                    s.x += v.x * scale[b] * ww.x; s.y += v.y * scale[b] * ww.y; s.z += v.z * scale[b] * ww.z; s.w += v.w * scale[b] * ww.w;
+                }
+            }
+            acc.x += s.x; acc.y += s.y; acc.z += s.z; acc.w += s.w;
+            *reinterpret_cast<float4*>(xr + i) = acc;
+        }
+        return;
+    }
     for (int b = 0; b < n_branches; ++b) {
         const float* row = br.b[b] + (size_t)r * width;
         float ss = 0.f;
         for (int i = threadIdx.x; i < width; i += blockDim.x) { const float v = row[i]; ss += v * v; }
         ss = block_sum(ss, scratch);
-        scale[b] = 1.0f / sqrtf(ss / (float)width + eps);
+        scale[b] = coef / sqrtf(ss / (float)width + eps);
     }
-    float* xr = x + (size_t)r * width;
     for (int i = threadIdx.x; i < width; i += blockDim.x) {
         float s = 0.f;
         for (int b = 0; b < n_branches; ++b) s += br.b[b][(size_t)r * width + i] * scale[b] * br.w[b][i];
-        float v = coef * s;
+        float v = s;
         if (extra) v += extra_coef * extra[(size_t)r * width + i];
         xr[i] += v;
     }
@@ -131,12 +199,20 @@ static inline unsigned flat_grid(size_t n) {
 extern "C" int imparo_act_rows(const void* x, void* out, int dtype, long long n, int kind, cudaStream_t stream) {
     if (n <= 0) return 0;
     if (kind < 0 || kind > 2) return -22;
-    if (dtype == IMPARO_DT_F32)
-        launch(act_rows_kernel<float>, dim3(flat_grid(n)), dim3(256), 0, stream, (const float*)x, (float*)out, (size_t)n, kind);
-    else if (dtype == IMPARO_DT_BF16)
-        launch(act_rows_kernel<__nv_bfloat16>, dim3(flat_grid(n)), dim3(256), 0, stream, (const __nv_bfloat16*)x,
-               (__nv_bfloat16*)out, (size_t)n, kind);
-    else return -1;
+    const bool aligned = (((uintptr_t)x | (uintptr_t)out) & 15) == 0;
+    if (dtype == IMPARO_DT_F32) {
+        if (aligned && n % 4 == 0)
+            launch(act_rows_vec_kernel<float>, dim3(flat_grid(n / 4)), dim3(256), 0, stream, (const float*)x, (float*)out, (size_t)(n / 4), kind);
+        else
+            launch(act_rows_kernel<float>, dim3(flat_grid(n)), dim3(256), 0, stream, (const float*)x, (float*)out, (size_t)n, kind);
+    } else if (dtype == IMPARO_DT_BF16) {
+        if (aligned && n % 8 == 0)
+            launch(act_rows_vec_kernel<__nv_bfloat16>, dim3(flat_grid(n / 8)), dim3(256), 0, stream, (const __nv_bfloat16*)x,
+                   (__nv_bfloat16*)out, (size_t)(n / 8), kind);
+        else
+            launch(act_rows_kernel<__nv_bfloat16>, dim3(flat_grid(n)), dim3(256), 0, stream, (const __nv_bfloat16*)x,
+                   (__nv_bfloat16*)out, (size_t)n, kind);
+    } else return -1;
     IMPARO_CHECK_LAUNCH();
     return 0;
 }
@@ -145,12 +221,13 @@ extern "C" int imparo_gated_rmsnorm(const float* o, const float* w, float eps, c
                                     void* out, int dtype, int n_rows, int width, cudaStream_t stream) {
     if (n_rows <= 0) return 0;
     const int threads = width >= 1024 ? 256 : 128;
+    const int vec = (width % 4 == 0 && (((uintptr_t)o | (uintptr_t)w) & 15) == 0) ? 1 : 0;
     if (dtype == IMPARO_DT_F32)
         launch(gated_rmsnorm_kernel<float>, dim3(n_rows), dim3(threads), 0, stream, o, w, eps, (const float*)gate,
-               (size_t)gate_stride, (float*)out, width);
+               (size_t)gate_stride, (float*)out, width, vec);
     else if (dtype == IMPARO_DT_BF16)
         launch(gated_rmsnorm_kernel<__nv_bfloat16>, dim3(n_rows), dim3(threads), 0, stream, o, w, eps,
-               (const __nv_bfloat16*)gate, (size_t)gate_stride, (__nv_bfloat16*)out, width);
+               (const __nv_bfloat16*)gate, (size_t)gate_stride, (__nv_bfloat16*)out, width, vec);
     else return -1;
     IMPARO_CHECK_LAUNCH();
     return 0;
@@ -162,9 +239,11 @@ extern "C" int imparo_norm_mean_add(float* x, int n_branches, const float* const
     if (n_rows <= 0) return 0;
     if (n_branches < 0 || n_branches > 4) return -2;
     Branches br = {};
-    for (int b = 0; b < n_branches; ++b) { br.b[b] = branches[b]; br.w[b] = weights[b]; }
+    uintptr_t all = (uintptr_t)x | (uintptr_t)extra;
+    for (int b = 0; b < n_branches; ++b) { br.b[b] = branches[b]; br.w[b] = weights[b]; all |= (uintptr_t)branches[b] | (uintptr_t)weights[b]; }
+    const int vec = (width % 4 == 0 && (all & 15) == 0) ? 1 : 0;
     launch(norm_mean_add_kernel, dim3(n_rows), dim3(width >= 1024 ? 256 : 128), 0, stream, x, br, n_branches, eps, coef, extra,
-           extra_coef, width);
+           extra_coef, width, vec);
     IMPARO_CHECK_LAUNCH();
     return 0;
 }
