@@ -215,26 +215,39 @@ template <bool SILU, bool SPLIT, typename F>
 __device__ __forceinline__ void stage(const bf16* __restrict__ src, size_t row_stride, int r_begin, int n, int width,
                                       bf16* __restrict__ dst, bf16* __restrict__ lo, int ld, F factor) {
     const int vecs = width / 8;
-    for (int idx = threadIdx.x; idx < C * vecs; idx += THREADS) {
-        const int r = idx / vecs, c = (idx - r * vecs) * 8;
-        uint4 hi4 = make_uint4(0u, 0u, 0u, 0u), lo4 = hi4;
-        if (r < n) {
-            const uint4 raw = *reinterpret_cast<const uint4*>(src + (size_t)(r_begin + r) * row_stride + c);
-            const bf16* e = reinterpret_cast<const bf16*>(&raw);
-            const float f = factor(r);
-            bf16* ho = reinterpret_cast<bf16*>(&hi4);
-            bf16* lw = reinterpret_cast<bf16*>(&lo4);
+    constexpr int U = 4;                                      // loads requested together per thread
+    for (int base = threadIdx.x; base < C * vecs; base += THREADS * U) {
+        uint4 raw[U];
 #pragma unroll
-            for (int u = 0; u < 8; ++u) {
-                float x = __bfloat162float(e[u]);
-                if (SILU) x = silu(x);
-                x *= f;
-                ho[u] = __float2bfloat16_rn(x);
-                if (SPLIT) lw[u] = __float2bfloat16_rn(x - __bfloat162float(ho[u]));
-            }
+        for (int u = 0; u < U; ++u) {
+            const int idx = base + u * THREADS;
+            const int r = idx / vecs, c = (idx - r * vecs) * 8;
+            raw[u] = make_uint4(0u, 0u, 0u, 0u);
+            if (idx < C * vecs && r < n) raw[u] = *reinterpret_cast<const uint4*>(src + (size_t)(r_begin + r) * row_stride + c);
         }
-        *reinterpret_cast<uint4*>(dst + (size_t)r * ld + c) = hi4;
-        if (SPLIT) *reinterpret_cast<uint4*>(lo + (size_t)r * ld + c) = lo4;
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const int idx = base + u * THREADS;
+            if (idx >= C * vecs) break;
+            const int r = idx / vecs, c = (idx - r * vecs) * 8;
+            uint4 hi4 = make_uint4(0u, 0u, 0u, 0u), lo4 = hi4;
+            if (r < n) {
+                const bf16* e = reinterpret_cast<const bf16*>(&raw[u]);
+                const float f = factor(r);
+                bf16* ho = reinterpret_cast<bf16*>(&hi4);
+                bf16* lw = reinterpret_cast<bf16*>(&lo4);
+#pragma unroll
+                for (int q = 0; q < 8; ++q) {
+                    float x = __bfloat162float(e[q]);
+                    if (SILU) x = silu_bf16(x);
+                    x *= f;
+                    ho[q] = __float2bfloat16_rn(x);
+                    if (SPLIT) lw[q] = __float2bfloat16_rn(x - __bfloat162float(ho[q]));
+                }
+            }
+            *reinterpret_cast<uint4*>(dst + (size_t)r * ld + c) = hi4;
+            if (SPLIT) *reinterpret_cast<uint4*>(lo + (size_t)r * ld + c) = lo4;
+        }
     }
 }
 
@@ -314,14 +327,27 @@ out_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k, const bf16* _
     {
         const float* src = chunk_state + ((size_t)g * heads + h) * dim * vdim;
         const int vecs = vdim / 4;
-        for (int idx = threadIdx.x; idx < dim * vecs; idx += THREADS) {
-            const int r = idx / vecs, c = (idx - r * vecs) * 4;
-            const float4 x = __ldcg(reinterpret_cast<const float4*>(src + (size_t)r * vdim + c));
-            const __nv_bfloat162 h01 = __floats2bfloat162_rn(x.x, x.y), h23 = __floats2bfloat162_rn(x.z, x.w);
-            const float2 f01 = __bfloat1622float2(h01), f23 = __bfloat1622float2(h23);
-            const __nv_bfloat162 l01 = __floats2bfloat162_rn(x.x - f01.x, x.y - f01.y), l23 = __floats2bfloat162_rn(x.z - f23.x, x.w - f23.y);
-            *reinterpret_cast<uint2*>(s_hi + (size_t)r * lds + c) = make_uint2(*reinterpret_cast<const uint32_t*>(&h01), *reinterpret_cast<const uint32_t*>(&h23));
-            *reinterpret_cast<uint2*>(s_lo + (size_t)r * lds + c) = make_uint2(*reinterpret_cast<const uint32_t*>(&l01), *reinterpret_cast<const uint32_t*>(&l23));
+        constexpr int U = 8;
+        for (int base = threadIdx.x; base < dim * vecs; base += THREADS * U) {
+            float4 xs[U];
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+                const int idx = base + u * THREADS;
+                const int r = idx / vecs, c = (idx - r * vecs) * 4;
+                xs[u] = idx < dim * vecs ? __ldcg(reinterpret_cast<const float4*>(src + (size_t)r * vdim + c)) : make_float4(0.f, 0.f, 0.f, 0.f);
+            }
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+                const int idx = base + u * THREADS;
+                if (idx >= dim * vecs) break;
+                const int r = idx / vecs, c = (idx - r * vecs) * 4;
+                const float4 x = xs[u];
+                const __nv_bfloat162 h01 = __floats2bfloat162_rn(x.x, x.y), h23 = __floats2bfloat162_rn(x.z, x.w);
+                const float2 f01 = __bfloat1622float2(h01), f23 = __bfloat1622float2(h23);
+                const __nv_bfloat162 l01 = __floats2bfloat162_rn(x.x - f01.x, x.y - f01.y), l23 = __floats2bfloat162_rn(x.z - f23.x, x.w - f23.y);
+                *reinterpret_cast<uint2*>(s_hi + (size_t)r * lds + c) = make_uint2(*reinterpret_cast<const uint32_t*>(&h01), *reinterpret_cast<const uint32_t*>(&h23));
+                *reinterpret_cast<uint2*>(s_lo + (size_t)r * lds + c) = make_uint2(*reinterpret_cast<const uint32_t*>(&l01), *reinterpret_cast<const uint32_t*>(&l23));
+            }
         }
     }
     __syncthreads();

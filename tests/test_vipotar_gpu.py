@@ -77,10 +77,10 @@ def plain_logits(name, requests, seed=1):
     return out
 
 
-def engine_for(name, dtype, steps, parallel=4, **kw):
+def engine_for(name, dtype, steps, parallel=4, page=None, **kw):
     from imparo_b200.engine import Engine
-    page = PAGE[name]
-    max_tokens = traces.max_live_tokens(steps, 64)
+    page = page or PAGE[name]
+    max_tokens = traces.max_live_tokens(steps, max(64, page))        # a request holds whole pages
     return Engine(model_dir(name), dtype=dtype, ctx=max_tokens, parallel=parallel, page_size=page,
                   num_pages=(max_tokens + page - 1) // page, max_step_tokens=max(256, max_tokens), **kw)
 
@@ -103,7 +103,7 @@ def check_trace(engine, steps, name, requests, dtype, share=0.1):
 
 
 LENGTHS = {"A": [70, 45, 96, 33, 64, 51], "B": [5, 23, 40, 67, 90, 34], "C": [81, 40, 65, 97, 58], "D": [44, 71, 36, 60],
-           "E": [150, 47, 96, 201, 64], "F": [130, 75, 40, 164]}
+           "E": [150, 47, 96, 201, 64], "F": [130, 75, 40, 164], "G": [300, 140, 64, 411], "H": [520, 90, 270]}
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
@@ -116,6 +116,16 @@ def test_family(name, dtype, family):
     check_trace(engine_for(name, dtype, steps), steps, name, reqs, dtype)
     if family == "mixed":
         assert traces.max_live_tokens(steps) < sum(traces.round_up(len(t), 64) for t in reqs.values())
+
+
+@pytest.mark.parametrize("page", [16, 32, 64, 128])
+@pytest.mark.parametrize("name", ["E", "F", "G", "H"])
+def test_page_sizes_of_the_tensor_core_attention(name, page):
+    """bfloat16, heads of 64 and 128: the tcgen05 prompt kernel and the split-key kernel with every page size they take,
+    windows below and above a query tile, portions of up to 64 tokens beside decode rows."""
+    reqs = make_requests(name, LENGTHS[name][:3], seed=17)
+    steps = traces.mixed(reqs, seed=4, max_portion=64)
+    check_trace(engine_for(name, "bfloat16", steps, page=page), steps, name, reqs, "bfloat16")
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])

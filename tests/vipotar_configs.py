@@ -74,5 +74,21 @@ VIP_F = {
                       _right(2, 128, 128, (0.98, 0.999)), 384)] * 2,
 }
 
-ALL = {"A": VIP_A, "B": VIP_B, "C": VIP_C, "D": VIP_D, "E": VIP_E, "F": VIP_F}
-PAGE = {"A": 4, "B": 8, "C": 16, "D": 32, "E": 16, "F": 64}
+# windows wider than a query tile of the tensor-core kernels (128 rows), not multiples of a page or a tile
+VIP_G = {
+    "architecture": "Vipotar", "vocab": 280, "width": 128, "norm": {"eps": 1e-6}, "residual_mult": 0.5,
+    "layers": [_layer(_left(4, 1, 64, 64, 0.125, window=130, rot={"dims": 64, "base": 10000.0}), _right(2, 32, 64, (0.9, 0.99)), 192),
+               _layer(_left(4, 4, 64, 64, 0.125, window=72, rot={"dims": 16, "base": 10000.0}), _right(1, 64, 128, (0.999,)), 192)],
+}
+
+VIP_H = {
+    "architecture": "Vipotar", "vocab": 290, "width": 128, "norm": {"eps": 1e-6}, "residual_mult": 0.6, "logit_softcap": 25.0,
+    "loop": {"start": 0, "stop": 2, "times": 2},
+    "layers": [_layer(_left(4, 1, 128, 128, 0.09, window=257, rot={"dims": 32, "base": 500000.0,
+                                                                "scaling": {"factor": 2.0, "original": 128, "fast": 32.0, "slow": 1.0}}),
+                      _right(2, 64, 64, (0.95, 0.999)), 160),
+               _layer(_left(8, 2, 128, 128, 0.09, rot={"dims": 128, "base": 1000.0}), _right(4, 16, 32, (0.5, 0.9, 0.99, 0.999)), None)],
+}
+
+ALL = {"A": VIP_A, "B": VIP_B, "C": VIP_C, "D": VIP_D, "E": VIP_E, "F": VIP_F, "G": VIP_G, "H": VIP_H}
+PAGE = {"A": 4, "B": 8, "C": 16, "D": 32, "E": 16, "F": 64, "G": 32, "H": 16}
