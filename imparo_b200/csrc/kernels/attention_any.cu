@@ -24,7 +24,7 @@ qkv_rotate_store_kernel(const T* __restrict__ qkv, const int* __restrict__ posit
                         const float* __restrict__ inv_freq, int n_rot, int interleaved, float magnitude,
                         T* __restrict__ q_out, T* __restrict__ k_cache, T* __restrict__ v_cache,
                         const int* __restrict__ table, int max_blocks, int page_size, int n_pages,
-                        int nh, int nkv, int hd, int vd, int* status) {
+                        int nh, int nkv, int hd, int vd, size_t in_width, int* status) {
     pdl_trigger();
     const int t = blockIdx.x;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -33,7 +33,6 @@ qkv_rotate_store_kernel(const T* __restrict__ qkv, const int* __restrict__ posit
     if (hh >= total) return;
     const int pos = positions[t];
     const bool is_q = hh < nh, is_k = !is_q && hh < nh + nkv;
-    const size_t in_width = (size_t)(nh + nkv) * hd + (size_t)nkv * vd;
     const T* src;
     T* dst = nullptr;
     int bad_page = 0;
@@ -158,24 +157,26 @@ attention_any_kernel(const T* __restrict__ q, const T* __restrict__ k_cache, con
 
 using namespace imparo;
 
-// qkv: [n_tok, nh*hd + nkv*hd + nkv*vd].  nkv == 0: queries only.
+// qkv: [n_tok, nh*hd + nkv*hd + nkv*vd] in rows of row_stride elements (a stretch of a wider product).  nkv == 0: queries only.
 extern "C" int imparo_qkv_rotate_store(const void* qkv, int dtype, const int* positions, const int* item_of_token,
                                        const float* inv_freq, int n_rot, int interleaved, float magnitude,
                                        void* q_out, void* k_cache, void* v_cache,
                                        const int* table, int max_blocks, int page_size, int n_pages,
-                                       int n_tok, int nh, int nkv, int hd, int vd, int* status, cudaStream_t stream) {
+                                       int n_tok, int nh, int nkv, int hd, int vd, long long row_stride, int* status,
+                                       cudaStream_t stream) {
     if (n_tok <= 0) return 0;
     if (hd < 1 || hd > ANY_MAX_HEAD || vd < 1 || vd > ANY_MAX_HEAD) return -3;
     if (n_rot < 0 || n_rot > hd || (n_rot & 1)) return -4;
+    if (row_stride < (long long)(nh + nkv) * hd + (long long)nkv * vd) return -2;
     dim3 grid(n_tok, (nh + 2 * nkv + ANY_WARPS - 1) / ANY_WARPS);
     if (dtype == IMPARO_DT_F32)
         launch(qkv_rotate_store_kernel<float>, grid, dim3(ANY_WARPS * 32), 0, stream, (const float*)qkv, positions, item_of_token,
                inv_freq, n_rot, interleaved, magnitude, (float*)q_out, (float*)k_cache, (float*)v_cache, table, max_blocks,
-               page_size, n_pages, nh, nkv, hd, vd, status);
+               page_size, n_pages, nh, nkv, hd, vd, (size_t)row_stride, status);
     else if (dtype == IMPARO_DT_BF16)
         launch(qkv_rotate_store_kernel<__nv_bfloat16>, grid, dim3(ANY_WARPS * 32), 0, stream, (const __nv_bfloat16*)qkv, positions,
                item_of_token, inv_freq, n_rot, interleaved, magnitude, (__nv_bfloat16*)q_out, (__nv_bfloat16*)k_cache,
-               (__nv_bfloat16*)v_cache, table, max_blocks, page_size, n_pages, nh, nkv, hd, vd, status);
+               (__nv_bfloat16*)v_cache, table, max_blocks, page_size, n_pages, nh, nkv, hd, vd, (size_t)row_stride, status);
     else return -1;
     IMPARO_CHECK_LAUNCH();
     return 0;

@@ -44,6 +44,30 @@ __global__ void act_rows_vec_kernel(const T* x, T* out, size_t n_vec, int kind) 
     }
 }
 
+// out[r, :] = act(x[r, :]) for rows of x that are a stretch of wider rows (x_stride elements apart); out is dense.
+// VEC: 16 bytes at a time (width and x_stride multiples of the vector, both pointers 16-byte aligned)
+template <typename T, bool VEC>
+__global__ void act_rows_strided_kernel(const T* __restrict__ x, size_t x_stride, T* __restrict__ out, int n_rows, int width, int kind) {
+    constexpr int N = VEC ? 16 / (int)sizeof(T) : 1;
+    pdl_trigger();
+    pdl_wait();
+    const int per_row = width / N;
+    const size_t total = (size_t)n_rows * per_row;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+        const size_t r = i / per_row;
+        const int c = (int)(i - r * per_row) * N;
+        if (VEC) {
+            uint4 raw = *reinterpret_cast<const uint4*>(x + r * x_stride + c);
+            T* e = reinterpret_cast<T*>(&raw);
+#pragma unroll
+            for (int u = 0; u < N; ++u) e[u] = from_f32<T>(act_apply(to_f32(e[u]), kind));
+            *reinterpret_cast<uint4*>(out + r * width + c) = raw;
+        } else {
+            out[r * width + c] = from_f32<T>(act_apply(to_f32(x[r * x_stride + c]), kind));
+        }
+    }
+}
+
 // out[r, :] = o[r, :] / rms(o[r, :]) * w * sigmoid(gate[r, :]);  o is 32-bit, gate rows have their own stride
 template <typename T>
 __global__ void gated_rmsnorm_kernel(const float* __restrict__ o, const float* __restrict__ w, float eps,
@@ -213,6 +237,24 @@ extern "C" int imparo_act_rows(const void* x, void* out, int dtype, long long n,
             launch(act_rows_kernel<__nv_bfloat16>, dim3(flat_grid(n)), dim3(256), 0, stream, (const __nv_bfloat16*)x,
                    (__nv_bfloat16*)out, (size_t)n, kind);
     } else return -1;
+    IMPARO_CHECK_LAUNCH();
+    return 0;
+}
+
+extern "C" int imparo_act_rows_strided(const void* x, long long x_stride, void* out, int dtype, int n_rows, int width, int kind,
+                                       cudaStream_t stream) {
+    if (n_rows <= 0 || width <= 0) return 0;
+    if (kind < 0 || kind > 2) return -22;
+    if (x_stride < width) return -2;
+    const int es = dtype == IMPARO_DT_F32 ? 4 : 2, nvec = 16 / es;
+    const bool vec = width % nvec == 0 && x_stride % nvec == 0 && (((uintptr_t)x | (uintptr_t)out) & 15) == 0;
+    const size_t total = (size_t)n_rows * (vec ? width / nvec : width);
+#define IMPARO_ACT(T_, V_) launch(act_rows_strided_kernel<T_, V_>, dim3(flat_grid(total)), dim3(256), 0, stream, (const T_*)x, \
+        (size_t)x_stride, (T_*)out, n_rows, width, kind)
+    if (dtype == IMPARO_DT_F32) { if (vec) IMPARO_ACT(float, true); else IMPARO_ACT(float, false); }
+    else if (dtype == IMPARO_DT_BF16) { if (vec) IMPARO_ACT(__nv_bfloat16, true); else IMPARO_ACT(__nv_bfloat16, false); }
+    else return -1;
+#undef IMPARO_ACT
     IMPARO_CHECK_LAUNCH();
     return 0;
 }

@@ -111,7 +111,8 @@ def _declare_kernels(lib):
     _declare(lib, "imparo_add_scaled", [P, P, c_float, c_int64, S])
     _declare(lib, "imparo_stream_inject", [P, P, I, P, P, I, I, I, P, S])
     _declare(lib, "imparo_softcap", [P, c_int64, c_float, S])
-    _declare(lib, "imparo_qkv_rotate_store", [P, I, P, P, P, I, I, c_float, P, P, P, P, I, I, I, I, I, I, I, I, P, S])
+    _declare(lib, "imparo_qkv_rotate_store", [P, I, P, P, P, I, I, c_float, P, P, P, P, I, I, I, I, I, I, I, I, c_int64, P, S])
+    _declare(lib, "imparo_act_rows_strided", [P, c_int64, P, I, I, I, I, S])
     _declare(lib, "imparo_attention_any", [P, P, P, I, P, P, P, I, I, I, I, c_float, I, P, I, I, I, I, I, P, S])
     _declare(lib, "imparo_linear_attention_recurrent", [P, P, P, c_int64, I, I, P, P, P, P, I, I, P, I, I, I, P, S])
     _declare(lib, "imparo_linear_attention_chunked", [P, P, P, c_int64, I, I, P, P, P, I, I, P, P, I, I, P, I, I, I, P, S])

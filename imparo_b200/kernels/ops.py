@@ -953,10 +953,16 @@ ACTIVATIONS = {"relu2": 0, "gelu_tanh": 1, "silu": 2}
 
 
 def activation(x: torch.Tensor, out: torch.Tensor, kind: str) -> None:
-    """out = act(x) elementwise (relu2: relu(x)^2, gelu_tanh, silu); out may be x."""
-    _cuda(x, out)
+    """out = act(x) elementwise (relu2: relu(x)^2, gelu_tanh, silu); out may be x.  x may be a [rows, width] stretch of
+    wider rows (a column range of a product that several consumers share); out is then dense [rows, width]."""
     _need(kind in ACTIVATIONS, f"activation: unknown kind '{kind}' (known: {', '.join(sorted(ACTIVATIONS))})")
     _need(x.shape == out.shape and x.dtype == out.dtype, "activation: out must match x")
+    if x.dim() == 2 and not x.is_contiguous():
+        _need(x.is_cuda and out.is_cuda and out.is_contiguous() and x.stride(1) == 1, "activation: rows of x must be dense")
+        _check(_lib.kernels().imparo_act_rows_strided(_ptr(x), x.stride(0), _ptr(out), _code(x), x.shape[0], x.shape[1],
+                                                      ACTIVATIONS[kind], _stream()), "activation")
+        return
+    _cuda(x, out)
     _check(_lib.kernels().imparo_act_rows(_ptr(x), _ptr(out), _code(x), x.numel(), ACTIVATIONS[kind], _stream()), "activation")
 
 
@@ -1028,8 +1034,10 @@ def qkv_rotate_store(qkv, positions, item_of_token, inv_freq, n_rot, interleaved
                      table, page_size, n_pages, nh, nkv, hd, vd, status) -> None:
     """qkv [T, nh*hd + nkv*hd + nkv*vd] -> q_out [T, nh*hd] rotated; k rotated and v written into their pages
     (K rows nkv*hd wide, V rows nkv*vd wide).  Rotation over the first n_rot dims: pairs (2i, 2i+1) when interleaved,
-    else (i, i + n_rot/2); sines and cosines times magnitude.  nkv == 0: queries only."""
-    _cuda(qkv, positions, item_of_token, inv_freq, q_out, k_cache, v_cache, table, status)
+    else (i, i + n_rot/2); sines and cosines times magnitude.  nkv == 0: queries only.  qkv may be a column range of a
+    wider product (rows dense, any row stride)."""
+    _need(qkv.is_cuda and qkv.stride(1) == 1, "qkv_rotate_store: rows of qkv must be dense CUDA memory")
+    _cuda(positions, item_of_token, inv_freq, q_out, k_cache, v_cache, table, status)
     T = q_out.shape[0]
     _need(tuple(qkv.shape) == (T, nh * hd + nkv * (hd + vd)) and q_out.shape[1] == nh * hd and qkv.dtype == q_out.dtype,
           "qkv_rotate_store: widths")
@@ -1045,7 +1053,7 @@ def qkv_rotate_store(qkv, positions, item_of_token, inv_freq, n_rot, interleaved
     _check(_lib.kernels().imparo_qkv_rotate_store(
         _ptr(qkv), _code(q_out), _ptr(positions), _ptr(item_of_token), _ptr(inv_freq), int(n_rot), int(bool(interleaved)),
         float(magnitude), _ptr(q_out), _ptr(k_cache), _ptr(v_cache), _ptr(table), table.shape[1] if table is not None else 0,
-        page_size, n_pages, T, nh, nkv, hd, vd, _ptr(status), _stream()), "qkv_rotate_store")
+        page_size, n_pages, T, nh, nkv, hd, vd, qkv.stride(0), _ptr(status), _stream()), "qkv_rotate_store")
 
 
 def attention_any(q, k_cache, v_cache, positions, item_of_token, table, page_size, n_pages, window, scale, sink,

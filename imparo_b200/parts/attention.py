@@ -114,14 +114,26 @@ class AttentionMixer(Part):
         context = max(int(upper_context), min(most.get("context", 0), 1 << 17))
         return (8 * ops.sm_count() + rows * self.nkv * (1 + -(-context // 512))) * (self.nh // self.nkv)
 
-    def _forward_general(self, x, batch, kv, residual, accumulate):
-        """Unfused: product, rotation + cache write, attention (one warp per token and head), output product."""
+    def input_rows(self) -> int:
+        return self.nh * self.hd + self.nkv * (self.hd + self.vd) if self.general else 0
+
+    def input_weight(self):
+        return self.w_qkv
+
+    def adopt_input_weight(self, view) -> None:
+        self.w_qkv = view
+
+    def _forward_general(self, x, batch, kv, residual, accumulate, projected=None):
+        """Product (unless the arrangement made it), rotation + cache write, attention, output product."""
         rt, T = self.rt, x.shape[0]
         nh, hd, vd = self.nh, self.hd, self.vd
         nkv = self.nkv if kv.writes else 0
         width = nh * hd + nkv * (hd + vd)
-        qkv = rt.workspace.get("attn_qkv", (T, width), rt.act_dtype, first="tokens")
-        ops.linear(x, self.w_qkv[:width], qkv, status=rt.status)
+        if projected is not None and kv.writes:
+            qkv = projected
+        else:
+            qkv = rt.workspace.get("attn_qkv", (T, width), rt.act_dtype, first="tokens")
+            ops.linear(x, self.w_qkv[:width], qkv, status=rt.status)
         q = rt.workspace.get("attn_q", (T, nh * hd), rt.act_dtype, first="tokens")
         rot = self.position.rotary()
         inv_freq, n_rot = rot if rot is not None else (None, 0)
@@ -161,10 +173,10 @@ class AttentionMixer(Part):
                               self.scale, self.sink, out, nh, self.nkv, hd, vd, rt.status)
         ops.linear(out, self.w_o, residual, accumulate=accumulate, status=rt.status)
 
-    def forward(self, x, batch, caches, residual, accumulate=True):
+    def forward(self, x, batch, caches, residual, accumulate=True, projected=None):
         kv = caches[0]
         if self.general:
-            return self._forward_general(x, batch, kv, residual, accumulate)
+            return self._forward_general(x, batch, kv, residual, accumulate, projected)
         if not accumulate:
             residual.zero_()              # the specialised path's products add; the caller's buffer starts from nothing
         rt, T = self.rt, x.shape[0]

@@ -143,6 +143,15 @@ class Part:
     def cache_specs(self) -> Tuple:
         return ()
 
+    # -- sublayers that share their input (optional) ----------------------------------------------------------------
+    # A mixer or feed-forward whose first operation is a product W x of its input may let an arrangement in which several
+    # sublayers read the same input make ONE product for all of them: input_rows() says how many output columns its
+    # product has (0: it takes no part), input_weight() is that matrix after bind, adopt_input_weight(view) replaces it
+    # by a view into the arrangement's stacked matrix (so the weights exist once), and forward(..., projected=p) gets
+    # its columns p [tokens, input_rows()] (rows dense, a column range of the shared product) instead of computing them.
+    def input_rows(self) -> int:
+        return 0
+
 
 class Block(Part):
     """Base of the "block" kind: how a layer's parts are arranged.  The model calls

@@ -131,8 +131,27 @@ class ParallelResidualBlock(Block):
         return [w for p in self.parts for w in p.weight_specs()]
 
     def bind(self, tensors):
+        import inspect
+        import torch
         for p in self.parts:
             p.bind(tensors)
+        # One product for everything that reads the normed input (Part.input_rows): the mixer's first products and the
+        # feed-forward's, stacked; the parts keep views into the stacked matrix, so the weights exist once.
+        self.w_in, self._in_ranges = None, None
+        subs = [p for p in (self.mixer, self.ff) if p is not None]
+        takes = "projected" in inspect.signature(self.mixer.forward).parameters
+        if takes and all(p.input_rows() > 0 for p in subs) and (self.ff is None or self._one_pass):
+            ranges, at = [], 0
+            for p in subs:
+                at = (at + 7) // 8 * 8
+                ranges.append((at, p.input_rows()))
+                at += p.input_rows()
+            first = subs[0].input_weight()
+            w = torch.zeros((at, first.shape[1]), dtype=first.dtype, device=first.device)
+            for p, (a, n) in zip(subs, ranges):
+                w[a:a + n] = p.input_weight()
+                p.adopt_input_weight(w[a:a + n])
+            self.w_in, self._in_ranges = w, ranges
 
     def cache_specs(self):
         return self.mixer.cache_specs()
@@ -148,12 +167,22 @@ class ParallelResidualBlock(Block):
         if probe:
             probe("mixer_norm", h)
         kw = {"scale": self.scale} if self.scale != 1.0 else {}
+        if self.w_in is not None and not probe:
+            both = self.rt.workspace.get("block_in", (x.shape[0], self.w_in.shape[0]), self.rt.act_dtype, first="tokens")
+            ops.linear(h, self.w_in, both, status=self.rt.status)
+            ma, mn = self._in_ranges[0]
+            kw["projected"] = both[:, ma:ma + mn]
         if self._one_pass and not probe:
             y = self.rt.workspace.get("ffn_out", (x.shape[0], x.shape[1]), torch.float32, first="tokens")
-            self.ff.forward_into(h, y)
+            if self.w_in is not None:
+                fa, fn = self._in_ranges[1]
+                self.ff.forward_into(h, y, projected=both[:, fa:fa + fn])
+            else:
+                self.ff.forward_into(h, y)
             self.mixer.forward(h, batch, caches, x, extra=y, extra_scale=self.scale, **kw)
         else:
             self.mixer.forward(h, batch, caches, x, **kw)
+            kw.pop("projected", None)
             ops.settle(x)
             if probe:
                 probe("stream_mixer", x)

@@ -70,11 +70,23 @@ class DenseFeedForward(Part):
         self.w_up = tensors[self.names["up"]]
         self.w_down = tensors[self.names["down"]]
 
-    def forward_into(self, x, out):
+    def input_rows(self) -> int:
+        return self.ff
+
+    def input_weight(self):
+        return self.w_up
+
+    def adopt_input_weight(self, view) -> None:
+        self.w_up = view
+
+    def forward_into(self, x, out, projected=None):
         rt, T = self.rt, x.shape[0]
         h = rt.workspace.get("ffn_h", (T, self.ff), rt.act_dtype, first="tokens")
-        ops.linear(x, self.w_up, h, status=rt.status)
-        ops.activation(h, h, self.act)
+        if projected is not None:
+            ops.activation(projected, h, self.act)          # from the shared product's columns into a dense tensor
+        else:
+            ops.linear(x, self.w_up, h, status=rt.status)
+            ops.activation(h, h, self.act)
         ops.linear(h, self.w_down, out, status=rt.status)
 
     def forward(self, x, batch, residual, scale: float = 1.0):

@@ -60,12 +60,24 @@ class DecayLinearAttention(Part):
     def cache_specs(self):
         return (SlotState((self.heads, self.dim, self.vdim)),)
 
-    def forward(self, x, batch, caches, residual, accumulate=True):
+    def input_rows(self) -> int:
+        return 2 * self.heads * self.dim + 2 * self.heads * self.vdim
+
+    def input_weight(self):
+        return self.w_in
+
+    def adopt_input_weight(self, view) -> None:
+        self.w_in = view
+
+    def forward(self, x, batch, caches, residual, accumulate=True, projected=None):
         st = caches[0]
         rt, T = self.rt, x.shape[0]
         qk, vv = self.heads * self.dim, self.heads * self.vdim
-        proj = rt.workspace.get("linattn_in", (T, 2 * qk + 2 * vv), rt.act_dtype, first="tokens")
-        ops.linear(x, self.w_in, proj, status=rt.status)
+        if projected is not None:
+            proj = projected
+        else:
+            proj = rt.workspace.get("linattn_in", (T, 2 * qk + 2 * vv), rt.act_dtype, first="tokens")
+            ops.linear(x, self.w_in, proj, status=rt.status)
         o = rt.workspace.get("linattn_o", (T, vv), torch.float32, first="tokens")
         # long portions: the recurrence in chunks that run side by side (a row-by-row walk of a 2,048-token prompt is 2,048
         # dependent steps on a handful of warps); the chunk length follows the step's size, which is part of its shape

@@ -51,14 +51,44 @@ class SideBySideMixer(Part):
     def cache_specs(self):
         return tuple(s for b, _ in self.branches for s in b.cache_specs())
 
-    def forward(self, x, batch, caches, residual, scale: float = 1.0, extra=None, extra_scale: float = 0.0):
+    # the branches' first products as one (see Part.input_rows): columns in the branches' order, each branch's range
+    # starting at a multiple of 8 columns (16-byte rows for the consumers' vector loads)
+    def _ranges(self):
+        out, at = [], 0
+        for b, _ in self.branches:
+            n = b.input_rows()
+            at = (at + 7) // 8 * 8
+            out.append((at, n))
+            at += n
+        return out, at
+
+    def input_rows(self) -> int:
+        if any(b.input_rows() == 0 for b, _ in self.branches):
+            return 0
+        return self._ranges()[1]
+
+    def input_weight(self):
+        ranges, total = self._ranges()
+        first = self.branches[0][0].input_weight()
+        w = torch.zeros((total, first.shape[1]), dtype=first.dtype, device=first.device)
+        for (b, _), (at, n) in zip(self.branches, ranges):
+            w[at:at + n] = b.input_weight()
+        return w
+
+    def adopt_input_weight(self, view) -> None:
+        for (b, _), (at, n) in zip(self.branches, self._ranges()[0]):
+            b.adopt_input_weight(view[at:at + n])
+
+    def forward(self, x, batch, caches, residual, scale: float = 1.0, extra=None, extra_scale: float = 0.0, projected=None):
         """extra: a float32 [tokens, hidden] buffer added as well, times extra_scale, in the same pass over the
-        stream (the arrangement's other sublayer)."""
+        stream (the arrangement's other sublayer).  projected: the branches' first products, made by the arrangement."""
         rt, T = self.rt, x.shape[0]
         outs, at = [], 0
+        ranges = self._ranges()[0] if projected is not None else None
         for i, (b, _) in enumerate(self.branches):
             buf = rt.workspace.get(f"branch_out_{i}", (T, self.hidden), torch.float32, first="tokens")
-            b.forward(x, batch, caches[at:at + self._n_caches[i]], buf, accumulate=False)
+            kw = {} if projected is None else {"projected": projected[:, ranges[i][0]:ranges[i][0] + ranges[i][1]]}
+            b.forward(x, batch, caches[at:at + self._n_caches[i]], buf, accumulate=False, **kw)
             at += self._n_caches[i]
             outs.append(buf)
         ops.norm_mean_add(residual, outs, self.norm_w, self.eps, scale / len(outs), extra, extra_scale)
