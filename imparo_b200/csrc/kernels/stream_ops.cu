@@ -171,6 +171,67 @@ __global__ void norm_mean_add_kernel(float* __restrict__ x, Branches br, int n_b
     }
 }
 
+// The same, and then the RMS norm of the updated row with weight nw into out (the next layer's normed input): the
+// stream is read and written once for both.  A thread norms the elements it wrote itself.
+template <typename TOut>
+__global__ void norm_mean_add_rmsnorm_kernel(float* __restrict__ x, Branches br, int n_branches, float eps, float coef,
+                                             const float* __restrict__ extra, float extra_coef, int width, int vec,
+                                             const float* __restrict__ nw, float neps, TOut* __restrict__ out) {
+    __shared__ float scratch[33];
+    pdl_trigger();
+    pdl_wait();
+    const int r = blockIdx.x;
+    float scale[4] = {0.f, 0.f, 0.f, 0.f};
+    float* xr = x + (size_t)r * width;
+    TOut* orow = out + (size_t)r * width;
+    const int step = vec ? 4 : 1;
+    {
+        float ss[4] = {0.f, 0.f, 0.f, 0.f};
+        for (int i = threadIdx.x * step; i < width; i += blockDim.x * step) {
+#pragma unroll
+            for (int b = 0; b < 4; ++b) {
+                if (b < n_branches) {
+                    const float* p = br.b[b] + (size_t)r * width + i;
+                    if (vec) { const float4 v = *reinterpret_cast<const float4*>(p); ss[b] += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w; }
+                    else ss[b] += p[0] * p[0];
+                }
+            }
+        }
+#pragma unroll
+        for (int b = 0; b < 4; ++b)
+            if (b < n_branches) scale[b] = coef / sqrtf(block_sum(ss[b], scratch) / (float)width + eps);
+    }
+    float ss2 = 0.f;
+    for (int i = threadIdx.x * step; i < width; i += blockDim.x * step) {
+        float acc[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) acc[u] = u < step ? xr[i + u] : 0.f;
+        if (extra) {
+#pragma unroll
+            for (int u = 0; u < 4; ++u) if (u < step) acc[u] += extra_coef * extra[(size_t)r * width + i + u];
+        }
+        float s[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+        for (int b = 0; b < 4; ++b) {
+            if (b < n_branches) {
+#pragma unroll
+                for (int u = 0; u < 4; ++u)
+                    if (u < step) s[u] += br.b[b][(size_t)r * width + i + u] * scale[b] * br.w[b][i + u];
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            if (u < step) { acc[u] += s[u]; xr[i + u] = acc[u]; ss2 += acc[u] * acc[u]; }
+        }
+    }
+    const float nscale = 1.0f / sqrtf(block_sum(ss2, scratch) / (float)width + neps);
+    for (int i = threadIdx.x * step; i < width; i += blockDim.x * step) {
+#pragma unroll
+        for (int u = 0; u < 4; ++u)
+            if (u < step) orow[i + u] = from_f32<TOut>(xr[i + u] * nscale * nw[i + u]);
+    }
+}
+
 __global__ void add_scaled_kernel(float* __restrict__ x, const float* __restrict__ y, float coef, size_t n) {
     pdl_trigger();
     pdl_wait();
@@ -286,6 +347,27 @@ extern "C" int imparo_norm_mean_add(float* x, int n_branches, const float* const
     const int vec = (width % 4 == 0 && (all & 15) == 0) ? 1 : 0;
     launch(norm_mean_add_kernel, dim3(n_rows), dim3(width >= 1024 ? 256 : 128), 0, stream, x, br, n_branches, eps, coef, extra,
            extra_coef, width, vec);
+    IMPARO_CHECK_LAUNCH();
+    return 0;
+}
+
+extern "C" int imparo_norm_mean_add_rmsnorm(float* x, int n_branches, const float* const* branches, const float* const* weights,
+                                            float eps, float coef, const float* extra, float extra_coef, const float* nw,
+                                            float neps, void* out, int out_dtype, int n_rows, int width, cudaStream_t stream) {
+    if (n_rows <= 0) return 0;
+    if (n_branches < 0 || n_branches > 4) return -2;
+    Branches br = {};
+    uintptr_t all = (uintptr_t)x | (uintptr_t)extra;
+    for (int b = 0; b < n_branches; ++b) { br.b[b] = branches[b]; br.w[b] = weights[b]; all |= (uintptr_t)branches[b] | (uintptr_t)weights[b]; }
+    const int vec = (width % 4 == 0 && (all & 15) == 0) ? 1 : 0;
+    const dim3 block(width >= 1024 ? 256 : 128);
+    if (out_dtype == IMPARO_DT_F32)
+        launch(norm_mean_add_rmsnorm_kernel<float>, dim3(n_rows), block, 0, stream, x, br, n_branches, eps, coef, extra, extra_coef,
+               width, vec, nw, neps, (float*)out);
+    else if (out_dtype == IMPARO_DT_BF16)
+        launch(norm_mean_add_rmsnorm_kernel<__nv_bfloat16>, dim3(n_rows), block, 0, stream, x, br, n_branches, eps, coef, extra,
+               extra_coef, width, vec, nw, neps, (__nv_bfloat16*)out);
+    else return -1;
     IMPARO_CHECK_LAUNCH();
     return 0;
 }

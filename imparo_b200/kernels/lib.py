@@ -108,6 +108,7 @@ def _declare_kernels(lib):
     _declare(lib, "imparo_act_rows", [P, P, I, c_int64, I, S])
     _declare(lib, "imparo_gated_rmsnorm", [P, P, c_float, P, c_int64, P, I, I, I, S])
     _declare(lib, "imparo_norm_mean_add", [P, I, P, P, c_float, c_float, P, c_float, I, I, S])
+    _declare(lib, "imparo_norm_mean_add_rmsnorm", [P, I, P, P, c_float, c_float, P, c_float, P, c_float, P, I, I, I, S])
     _declare(lib, "imparo_add_scaled", [P, P, c_float, c_int64, S])
     _declare(lib, "imparo_stream_inject", [P, P, I, P, P, I, I, I, P, S])
     _declare(lib, "imparo_softcap", [P, c_int64, c_float, S])

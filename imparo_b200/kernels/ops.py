@@ -76,6 +76,7 @@ class LaunchState:
         self.switches = switches if switches is not None else _default_switches()
         self.deferrable = set()      # data_ptr of streams whose next accumulate-product may stay pending
         self.pending = {}            # data_ptr -> (scratch, n_splits, rows, width)
+        self.pending_mean = {}       # data_ptr -> arguments of a norm_mean_add the next reader of the stream carries out
         self.partials = {}           # device index -> scratch of products into the stream
         self.consumer_parts = {}     # device index -> scratch of products a consumer kernel folds
         self.tc_scratch = {}         # device index -> (floats, counters) of the cluster-folded products
@@ -168,6 +169,7 @@ def selftest_wait_limit(status: torch.Tensor, limit: int = 1000) -> int:
 def embed_gather(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor, status: torch.Tensor) -> None:
     _cuda(table, ids, out, status)
     _S.pending.pop(out.data_ptr(), None)       # the stream starts afresh: partials of an unfinished step are void
+    _S.pending_mean.pop(out.data_ptr(), None)
     n, width = out.shape
     _need(ids.dtype == torch.int32 and ids.numel() >= n, "ids must be int32, one per output row")
     _need(out.dtype == torch.float32 and table.shape[1] == width, "embedding output is float32 [tokens, width]")
@@ -235,7 +237,10 @@ def disallow_deferred_add(stream: torch.Tensor) -> None:
 
 
 def settle(stream: torch.Tensor) -> None:
-    """Fold pending partials into the stream (no-op when there are none)."""
+    """Fold pending partials into the stream, carry out a pending norm_mean_add (no-op when there is none)."""
+    pm = _S.pending_mean.pop(stream.data_ptr(), None)
+    if pm is not None:
+        norm_mean_add(stream, *pm)
     p = _S.pending.pop(stream.data_ptr(), None)
     if p is not None:
         scratch, S, T, N = p
@@ -246,6 +251,20 @@ def settle(stream: torch.Tensor) -> None:
 def rmsnorm(x: torch.Tensor, w: torch.Tensor, eps: float, out: torch.Tensor,
             rows: Optional[torch.Tensor] = None) -> None:
     _cuda(x, w, out, rows)
+    pm = _S.pending_mean.get(x.data_ptr())
+    if pm is not None:
+        if rows is None and out.shape == x.shape and w.numel() == x.shape[1] and w.dtype == torch.float32:
+            # the add that was left pending and the norm of the updated rows in one pass over the stream
+            import ctypes
+            _S.pending_mean.pop(x.data_ptr())
+            branches, weights, b_eps, coef, extra, extra_coef = pm
+            bp = (ctypes.c_void_p * 4)(*[b.data_ptr() for b in branches])
+            wp = (ctypes.c_void_p * 4)(*[t.data_ptr() for t in weights])
+            _check(_lib.kernels().imparo_norm_mean_add_rmsnorm(_ptr(x), len(branches), bp, wp, float(b_eps), float(coef), _ptr(extra),
+                                                               float(extra_coef), _ptr(w), float(eps), _ptr(out), _code(out),
+                                                               x.shape[0], x.shape[1], _stream()), "norm_mean_add_rmsnorm")
+            return
+        settle(x)
     pend = _S.pending.get(x.data_ptr())
     if pend is not None:
         scratch, S, T, N = pend
@@ -979,11 +998,18 @@ def gated_rmsnorm(o: torch.Tensor, w: torch.Tensor, eps: float, gate: torch.Tens
 
 
 def norm_mean_add(x: torch.Tensor, branches, weights, eps: float, coef: float, extra: Optional[torch.Tensor] = None,
-                  extra_coef: float = 0.0) -> None:
+                  extra_coef: float = 0.0, defer: bool = False) -> None:
     """x += coef * sum_b rms(branches[b]) * weights[b] + extra_coef * extra, row by row; all float32 [rows, width],
-    up to four branches."""
+    up to four branches.
+
+    defer: when the caller of this part has promised (allow_deferred_add) that whatever reads x next goes through
+    ops.rmsnorm, ops.settle or another launcher that settles, the add is only noted; ops.rmsnorm then carries it out and
+    norms the updated rows in the same kernel.  The branches and extra must stay untouched until then."""
     import ctypes
     settle(x)
+    if defer and x.data_ptr() in _S.deferrable and x.is_contiguous():
+        _S.pending_mean[x.data_ptr()] = (list(branches), list(weights), eps, coef, extra, extra_coef)
+        return
     _cuda(x, extra, *branches, *weights)
     n, width = x.shape
     _need(1 <= len(branches) <= 4 and len(weights) == len(branches), "norm_mean_add: one to four branches, a weight each")

@@ -160,10 +160,10 @@ class ParallelResidualBlock(Block):
         from ..kernels import ops
         import torch
         probe = self.rt.probe if self.rt.probe_now else None
-        ops.settle(x)
         if probe:
+            ops.settle(x)
             probe("stream_in", x)
-        h = self.norm.forward(x, tag="normed_mixer")
+        h = self.norm.forward(x, tag="normed_mixer")          # (carries out an add the block before left pending)
         if probe:
             probe("mixer_norm", h)
         kw = {"scale": self.scale} if self.scale != 1.0 else {}
@@ -179,15 +179,20 @@ class ParallelResidualBlock(Block):
                 self.ff.forward_into(h, y, projected=both[:, fa:fa + fn])
             else:
                 self.ff.forward_into(h, y)
-            self.mixer.forward(h, batch, caches, x, extra=y, extra_scale=self.scale, **kw)
-        else:
-            self.mixer.forward(h, batch, caches, x, **kw)
-            kw.pop("projected", None)
-            ops.settle(x)
-            if probe:
-                probe("stream_mixer", x)
-            if self.ff is not None:
-                self.ff.forward(h, batch, x, **kw)
+            # the mixer's add is the block's last write to the stream: it may stay pending for the next norm
+            ops.allow_deferred_add(x)
+            try:
+                self.mixer.forward(h, batch, caches, x, extra=y, extra_scale=self.scale, **kw)
+            finally:
+                ops.disallow_deferred_add(x)
+            return None
+        self.mixer.forward(h, batch, caches, x, **kw)
+        kw.pop("projected", None)
+        ops.settle(x)
+        if probe:
+            probe("stream_mixer", x)
+        if self.ff is not None:
+            self.ff.forward(h, batch, x, **kw)
         ops.settle(x)
         if probe:
             probe("stream_out", x)

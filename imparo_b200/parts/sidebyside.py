@@ -91,4 +91,5 @@ class SideBySideMixer(Part):
             b.forward(x, batch, caches[at:at + self._n_caches[i]], buf, accumulate=False, **kw)
             at += self._n_caches[i]
             outs.append(buf)
-        ops.norm_mean_add(residual, outs, self.norm_w, self.eps, scale / len(outs), extra, extra_scale)
+        # (the add may stay pending for the next norm of the stream to carry out: ops.allow_deferred_add by the arrangement)
+        ops.norm_mean_add(residual, outs, self.norm_w, self.eps, scale / len(outs), extra, extra_scale, defer=True)
