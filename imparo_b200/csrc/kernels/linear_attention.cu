@@ -311,22 +311,24 @@ out_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k, const bf16* _
     pdl_wait();
     if (!found) return;
     const int n = r_end - r_begin;
-    const int ldq = dim + PAD, ldv = vdim + PAD, lds = vdim + PAD, ldaf = C + 4, ldab = C + PAD, ldp = 20;
+    // the value columns are shared out over the grid's z extent (each CTA computes the chunk's scores itself): half the
+    // state and half of v per CTA, so that two CTAs fit an SM
+    const int vcols = vdim / (int)gridDim.z, v0 = (int)blockIdx.z * vcols;
+    const int ldq = dim + PAD, ldv = vcols + PAD, lds = vcols + PAD, ldab = C + PAD, ldp = 20;
     bf16* q_s = reinterpret_cast<bf16*>(lt_smem);
     bf16* k_s = q_s + C * ldq;
     bf16* v_s = k_s + C * ldq;
     bf16* s_hi = v_s + C * ldv;
     bf16* s_lo = s_hi + dim * lds;
     bf16* a_bf = s_lo + dim * lds;
-    float* a_f = reinterpret_cast<float*>(a_bf + C * ldab);
-    float* patch = a_f + C * ldaf + (threadIdx.x >> 5) * 16 * ldp;
+    float* patch = reinterpret_cast<float*>(a_bf + C * ldab) + (threadIdx.x >> 5) * 16 * ldp;
     auto one = [](int) { return 1.f; };
     stage<SILU, false>(q + (size_t)h * dim, row_stride, r_begin, n, dim, q_s, nullptr, ldq, one);
     stage<SILU, false>(k + (size_t)h * dim, row_stride, r_begin, n, dim, k_s, nullptr, ldq, one);
-    stage<SILU, false>(v + (size_t)h * vdim, row_stride, r_begin, n, vdim, v_s, nullptr, ldv, one);
+    stage<SILU, false>(v + (size_t)h * vdim + v0, row_stride, r_begin, n, vcols, v_s, nullptr, ldv, one);
     {
-        const float* src = chunk_state + ((size_t)g * heads + h) * dim * vdim;
-        const int vecs = vdim / 4;
+        const float* src = chunk_state + ((size_t)g * heads + h) * dim * vdim + v0;
+        const int vecs = vcols / 4;
         constexpr int U = 8;
         for (int base = threadIdx.x; base < dim * vecs; base += THREADS * U) {
             float4 xs[U];
@@ -352,8 +354,9 @@ out_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k, const bf16* _
     }
     __syncthreads();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int kts = dim / 16, vts = vdim / 16;
-    // scores of the tiles on and below the diagonal: (0,0) (1,0) (1,1) (2,0) ... (3,3)
+    const int kts = dim / 16, vts = vcols / 16;
+    // scores of the tiles on and below the diagonal: (0,0) (1,0) (1,1) (2,0) ... (3,3); each goes through the warp's patch,
+    // where it is multiplied by the decay powers in 32-bit and masked, into the bfloat16 operand of the product with v
     for (int t = warp; t < 10; t += THREADS / 32) {
         int it = 0, jt = t;
         while (jt > it) { jt -= it + 1; ++it; }
@@ -366,13 +369,14 @@ out_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k, const bf16* _
             wm::load_matrix_sync(b, k_s + (size_t)jt * 16 * ldq + kk * 16, ldq);
             wm::mma_sync(acc, a, b, acc);
         }
-        wm::store_matrix_sync(a_f + (size_t)it * 16 * ldaf + jt * 16, acc, ldaf, wm::mem_row_major);
-    }
-    __syncthreads();
-    for (int idx = threadIdx.x; idx < C * C; idx += THREADS) {
-        const int i = idx / C, j = idx - i * C;
-        const float w = (j <= i && i < n) ? a_f[(size_t)i * ldaf + j] * pw[i - j] : 0.f;
-        a_bf[(size_t)i * ldab + j] = __float2bfloat16_rn(w);
+        wm::store_matrix_sync(patch, acc, ldp, wm::mem_row_major);
+        __syncwarp();
+        for (int e = lane; e < 256; e += 32) {
+            const int i = it * 16 + (e >> 4), j = jt * 16 + (e & 15);
+            const float w = (j <= i && i < n) ? patch[(e >> 4) * ldp + (e & 15)] * pw[i - j] : 0.f;
+            a_bf[(size_t)i * ldab + j] = __float2bfloat16_rn(w);
+        }
+        __syncwarp();
     }
     __syncthreads();
     for (int t = warp; t < 4 * vts; t += THREADS / 32) {
@@ -405,16 +409,16 @@ out_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k, const bf16* _
         __syncwarp();
         for (int e = lane; e < 256; e += 32) {
             const int r = it * 16 + (e >> 4);
-            if (r < n) out[(size_t)(r_begin + r) * ((size_t)heads * vdim) + (size_t)h * vdim + vt * 16 + (e & 15)] = patch[(e >> 4) * ldp + (e & 15)];
+            if (r < n) out[(size_t)(r_begin + r) * ((size_t)heads * vdim) + (size_t)h * vdim + v0 + vt * 16 + (e & 15)] = patch[(e >> 4) * ldp + (e & 15)];
         }
         __syncwarp();
     }
 }
 
 static size_t local_smem(int dim, int vdim) { return (size_t)C * (2 * (dim + PAD) + (vdim + PAD)) * 2; }
-static size_t out_smem(int dim, int vdim) {
-    return (size_t)C * (2 * (dim + PAD) + (vdim + PAD)) * 2 + (size_t)2 * dim * (vdim + PAD) * 2 + (size_t)C * (C + PAD) * 2 +
-           (size_t)C * (C + 4) * 4 + (size_t)(THREADS / 32) * 16 * 20 * 4;
+static size_t out_smem(int dim, int vcols) {                  // vcols: the value columns of one CTA
+    return (size_t)C * (2 * (dim + PAD) + (vcols + PAD)) * 2 + (size_t)2 * dim * (vcols + PAD) * 2 + (size_t)C * (C + PAD) * 2 +
+           (size_t)(THREADS / 32) * 16 * 20 * 4;
 }
 }  // namespace lt
 
@@ -480,9 +484,13 @@ extern "C" int imparo_linear_attention_chunked(const void* q, const void* k, con
         launch(linear_attention_scan_kernel, dim3(n_items, heads, (per_head_t + 255) / 256), dim3(256), 0, stream, decay, chunk_state, state,
                item_row_start, item_slot, n_items, n_slots, chunk, heads, per_head_t, status);
         IMPARO_CHECK_LAUNCH();
-        if (act_silu) launch(lt::out_kernel<true>, tgrid, dim3(lt::THREADS), lt::out_smem(dim, vdim), stream, qb, kb, vb, (size_t)row_stride,
+        // two CTAs per (chunk, head), half of the value columns each, when a half is still whole tiles with 16-byte rows
+        const int zsplit = (vdim >= 64 && vdim % 32 == 0) ? 2 : 1;
+        dim3 ogrid(max_chunks, heads, zsplit);
+        const size_t osmem = lt::out_smem(dim, vdim / zsplit);
+        if (act_silu) launch(lt::out_kernel<true>, ogrid, dim3(lt::THREADS), osmem, stream, qb, kb, vb, (size_t)row_stride,
                              decay, (const float*)chunk_state, item_row_start, n_items, out, heads, dim, vdim);
-        else launch(lt::out_kernel<false>, tgrid, dim3(lt::THREADS), lt::out_smem(dim, vdim), stream, qb, kb, vb, (size_t)row_stride,
+        else launch(lt::out_kernel<false>, ogrid, dim3(lt::THREADS), osmem, stream, qb, kb, vb, (size_t)row_stride,
                     decay, (const float*)chunk_state, item_row_start, n_items, out, heads, dim, vdim);
         IMPARO_CHECK_LAUNCH();
         return 0;

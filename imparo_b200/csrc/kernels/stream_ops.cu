@@ -202,34 +202,47 @@ __global__ void norm_mean_add_rmsnorm_kernel(float* __restrict__ x, Branches br,
             if (b < n_branches) scale[b] = coef / sqrtf(block_sum(ss[b], scratch) / (float)width + eps);
     }
     float ss2 = 0.f;
-    for (int i = threadIdx.x * step; i < width; i += blockDim.x * step) {
-        float acc[4];
-#pragma unroll
-        for (int u = 0; u < 4; ++u) acc[u] = u < step ? xr[i + u] : 0.f;
-        if (extra) {
-#pragma unroll
-            for (int u = 0; u < 4; ++u) if (u < step) acc[u] += extra_coef * extra[(size_t)r * width + i + u];
-        }
-        float s[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll
-        for (int b = 0; b < 4; ++b) {
-            if (b < n_branches) {
-#pragma unroll
-                for (int u = 0; u < 4; ++u)
-                    if (u < step) s[u] += br.b[b][(size_t)r * width + i + u] * scale[b] * br.w[b][i + u];
+    if (vec) {
+        for (int i = threadIdx.x * 4; i < width; i += blockDim.x * 4) {
+            float4 acc = *reinterpret_cast<const float4*>(xr + i);
+            if (extra) {
+                const float4 e = *reinterpret_cast<const float4*>(extra + (size_t)r * width + i);
+                acc.x += extra_coef * e.x; acc.y += extra_coef * e.y; acc.z += extra_coef * e.z; acc.w += extra_coef * e.w;
             }
-        }
+            float4 s = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
-        for (int u = 0; u < 4; ++u) {
-            if (u < step) { acc[u] += s[u]; xr[i + u] = acc[u]; ss2 += acc[u] * acc[u]; }
+            for (int b = 0; b < 4; ++b) {
+                if (b < n_branches) {
+                    const float4 v = *reinterpret_cast<const float4*>(br.b[b] + (size_t)r * width + i);
+                    const float4 ww = *reinterpret_cast<const float4*>(br.w[b] + i);
+                    s.x += v.x * scale[b] * ww.x; s.y += v.y * scale[b] * ww.y; s.z += v.z * scale[b] * ww.z; s.w += v.w * scale[b] * ww.w;
+                }
+            }
+            acc.x += s.x; acc.y += s.y; acc.z += s.z; acc.w += s.w;
+            *reinterpret_cast<float4*>(xr + i) = acc;
+            ss2 += acc.x * acc.x + acc.y * acc.y + acc.z * acc.z + acc.w * acc.w;
         }
+        const float nscale = 1.0f / sqrtf(block_sum(ss2, scratch) / (float)width + neps);
+        for (int i = threadIdx.x * 4; i < width; i += blockDim.x * 4) {
+            const float4 v = *reinterpret_cast<const float4*>(xr + i);
+            const float4 g = *reinterpret_cast<const float4*>(nw + i);
+            TOut* o = orow + i;
+            o[0] = from_f32<TOut>(v.x * nscale * g.x); o[1] = from_f32<TOut>(v.y * nscale * g.y);
+            o[2] = from_f32<TOut>(v.z * nscale * g.z); o[3] = from_f32<TOut>(v.w * nscale * g.w);
+        }
+        return;
+    }
+    for (int i = threadIdx.x; i < width; i += blockDim.x) {
+        float acc = xr[i];
+        if (extra) acc += extra_coef * extra[(size_t)r * width + i];
+        float sum = 0.f;
+        for (int b = 0; b < n_branches; ++b) sum += br.b[b][(size_t)r * width + i] * scale[b] * br.w[b][i];
+        acc += sum;
+        xr[i] = acc;
+        ss2 += acc * acc;
     }
     const float nscale = 1.0f / sqrtf(block_sum(ss2, scratch) / (float)width + neps);
-    for (int i = threadIdx.x * step; i < width; i += blockDim.x * step) {
-#pragma unroll
-        for (int u = 0; u < 4; ++u)
-            if (u < step) orow[i + u] = from_f32<TOut>(xr[i + u] * nscale * nw[i + u]);
-    }
+    for (int i = threadIdx.x; i < width; i += blockDim.x) orow[i] = from_f32<TOut>(xr[i] * nscale * nw[i]);
 }
 
 __global__ void add_scaled_kernel(float* __restrict__ x, const float* __restrict__ y, float coef, size_t n) {
