@@ -77,6 +77,76 @@ qkv_rotate_store_kernel(const T* __restrict__ qkv, const int* __restrict__ posit
     }
 }
 
+// Many tokens (a prompt portion), interleaved pairs, even head and value sizes, rows whose pairs are aligned: a block owns
+// one token; the position's sines and cosines are computed once and shared by all of the token's heads (the kernel above
+// computes them per head), and a lane moves a pair (2i, 2i+1) as one 4- or 8-byte word.
+template <typename T> struct Pair;
+template <> struct Pair<float> { using type = float2; };
+template <> struct Pair<__nv_bfloat16> { using type = __nv_bfloat162; };
+__device__ __forceinline__ float2 pair_f32(float2 v) { return v; }
+__device__ __forceinline__ float2 pair_f32(__nv_bfloat162 v) { return __bfloat1622float2(v); }
+template <typename P> __device__ __forceinline__ P pair_from(float a, float b);
+template <> __device__ __forceinline__ float2 pair_from<float2>(float a, float b) { return make_float2(a, b); }
+template <> __device__ __forceinline__ __nv_bfloat162 pair_from<__nv_bfloat162>(float a, float b) { return __floats2bfloat162_rn(a, b); }
+
+template <typename T>
+__global__ void __launch_bounds__(ANY_WARPS * 32)
+qkv_rotate_store_token_kernel(const T* __restrict__ qkv, const int* __restrict__ positions, const int* __restrict__ item_of_token,
+                              const float* __restrict__ inv_freq, int n_rot, float magnitude,
+                              T* __restrict__ q_out, T* __restrict__ k_cache, T* __restrict__ v_cache,
+                              const int* __restrict__ table, int max_blocks, int page_size, int n_pages,
+                              int nh, int nkv, int hd, int vd, size_t in_width, int* status) {
+    using P = typename Pair<T>::type;
+    __shared__ float sn_s[ANY_MAX_HEAD / 2], cs_s[ANY_MAX_HEAD / 2];
+    pdl_trigger();
+    const int t = blockIdx.x;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int pos = positions[t];
+    const int half = inv_freq ? (n_rot >> 1) : 0;
+    for (int i = threadIdx.x; i < half; i += blockDim.x) {
+        float sn, cs;
+        sincosf((float)pos * inv_freq[i], &sn, &cs);
+        sn_s[i] = sn * magnitude; cs_s[i] = cs * magnitude;
+    }
+    size_t cache_row = 0;
+    int page = 0;
+    if (nkv > 0) {
+        const int blk = pos / page_size;
+        page = blk < max_blocks ? table[(size_t)item_of_token[t] * max_blocks + blk] : -1;
+        if (page >= 0 && page < n_pages) cache_row = (size_t)page * page_size + (pos % page_size);
+    }
+    __syncthreads();
+    pdl_wait();
+    if (nkv > 0 && (page < 0 || page >= n_pages) && threadIdx.x == 0)
+        report(status, IMPARO_ST_PAGE_RANGE, 41, t, page);           // the token's keys and values are skipped, its queries written
+    const int total = nh + 2 * nkv;
+    const T* row = qkv + (size_t)t * in_width;
+    for (int hh = warp; hh < total; hh += ANY_WARPS) {
+        const bool is_q = hh < nh, is_k = !is_q && hh < nh + nkv;
+        const T* src;
+        T* dst;
+        int n;
+        if (is_q) {
+            src = row + (size_t)hh * hd;
+            dst = q_out + ((size_t)t * nh + hh) * hd;
+            n = hd;
+        } else {
+            if (page < 0 || page >= n_pages) continue;
+            const int kvh = is_k ? hh - nh : hh - nh - nkv;
+            n = is_k ? hd : vd;
+            src = row + (size_t)nh * hd + (is_k ? (size_t)kvh * hd : (size_t)nkv * hd + (size_t)kvh * vd);
+            dst = is_k ? k_cache + cache_row * ((size_t)nkv * hd) + (size_t)kvh * hd : v_cache + cache_row * ((size_t)nkv * vd) + (size_t)kvh * vd;
+        }
+        const int turn = (is_q || is_k) ? half : 0;
+        for (int i = lane; i < n / 2; i += 32) {
+            const float2 v = pair_f32(reinterpret_cast<const P*>(src)[i]);
+            float a = v.x, b = v.y;
+            if (i < turn) { a = v.x * cs_s[i] - v.y * sn_s[i]; b = v.y * cs_s[i] + v.x * sn_s[i]; }
+            reinterpret_cast<P*>(dst)[i] = pair_from<P>(a, b);
+        }
+    }
+}
+
 template <typename T>
 __global__ void __launch_bounds__(ANY_WARPS * 32)
 attention_any_kernel(const T* __restrict__ q, const T* __restrict__ k_cache, const T* __restrict__ v_cache,
@@ -168,6 +238,25 @@ extern "C" int imparo_qkv_rotate_store(const void* qkv, int dtype, const int* po
     if (hd < 1 || hd > ANY_MAX_HEAD || vd < 1 || vd > ANY_MAX_HEAD) return -3;
     if (n_rot < 0 || n_rot > hd || (n_rot & 1)) return -4;
     if (row_stride < (long long)(nh + nkv) * hd + (long long)nkv * vd) return -2;
+    {
+        // a prompt portion with interleaved pairs (or no rotation) whose pairs can be moved as words: a block per token
+        const int es = dtype == IMPARO_DT_F32 ? 4 : 2;
+        const bool words = hd % 2 == 0 && vd % 2 == 0 && row_stride % 2 == 0 &&
+                           (((uintptr_t)qkv | (uintptr_t)q_out | (uintptr_t)k_cache | (uintptr_t)v_cache) & (uintptr_t)(2 * es - 1)) == 0;
+        if (n_tok >= 256 && words && (interleaved || inv_freq == nullptr || n_rot == 0)) {
+            if (dtype == IMPARO_DT_F32)
+                launch(qkv_rotate_store_token_kernel<float>, dim3(n_tok), dim3(ANY_WARPS * 32), 0, stream, (const float*)qkv, positions,
+                       item_of_token, inv_freq, n_rot, magnitude, (float*)q_out, (float*)k_cache, (float*)v_cache, table, max_blocks,
+                       page_size, n_pages, nh, nkv, hd, vd, (size_t)row_stride, status);
+            else if (dtype == IMPARO_DT_BF16)
+                launch(qkv_rotate_store_token_kernel<__nv_bfloat16>, dim3(n_tok), dim3(ANY_WARPS * 32), 0, stream, (const __nv_bfloat16*)qkv,
+                       positions, item_of_token, inv_freq, n_rot, magnitude, (__nv_bfloat16*)q_out, (__nv_bfloat16*)k_cache,
+                       (__nv_bfloat16*)v_cache, table, max_blocks, page_size, n_pages, nh, nkv, hd, vd, (size_t)row_stride, status);
+            else return -1;
+            IMPARO_CHECK_LAUNCH();
+            return 0;
+        }
+    }
     dim3 grid(n_tok, (nh + 2 * nkv + ANY_WARPS - 1) / ANY_WARPS);
     if (dtype == IMPARO_DT_F32)
         launch(qkv_rotate_store_kernel<float>, grid, dim3(ANY_WARPS * 32), 0, stream, (const float*)qkv, positions, item_of_token,

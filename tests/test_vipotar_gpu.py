@@ -234,18 +234,20 @@ def _one_request_batch(T, page, start=0, n_pages=None):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("first", [45, 300])
 @pytest.mark.parametrize("nh,nkv,hd,vd,n_rot,window,scaled", [(4, 2, 16, 24, 8, 9, True), (6, 1, 24, 8, 0, None, False),
                                                               (3, 3, 32, 32, 32, 33, False), (8, 1, 96, 64, 48, 20, True),
                                                               (2, 1, 40, 200, 6, 7, False)])
-def test_rotation_window_and_sink_kernels(dtype, nh, nkv, hd, vd, n_rot, window, scaled):
-    """qkv_rotate_store + attention_any against the plain attention: a prompt of 45 tokens, then 30 tokens one by one
-    on the same cache (pages of 4: every border is crossed), sink on."""
+def test_rotation_window_and_sink_kernels(dtype, first, nh, nkv, hd, vd, n_rot, window, scaled):
+    """qkv_rotate_store + attention_any against the plain attention: a prompt of 45 or 300 tokens (the rotation kernel
+    of few tokens, and the one that gives a block to every token), then 30 tokens one by one on the same cache (pages of
+    4: every border is crossed), sink on."""
     import torch
     from imparo_b200.kernels import ops
     from imparo_b200.parts.position import RotaryInterleaved
     tdt = torch.float32 if dtype == "float32" else torch.bfloat16
     rng = np.random.default_rng(hd + vd)
-    T, page, W = 75, 4, 8
+    T, page, W = first + 30, 4, 8
     rot = None
     if n_rot:
         rot = {"dims": n_rot, "base": 300.0}
@@ -274,7 +276,7 @@ def test_rotation_window_and_sink_kernels(dtype, nh, nkv, hd, vd, n_rot, window,
     vc = torch.zeros(n_pages_total * page * nkv * vd, dtype=tdt, device="cuda")
     got = np.zeros((T, nh * vd))
     at = 0
-    for n in [45] + [1] * 30:
+    for n in [first] + [1] * 30:
         pos, iot, table, n_pages = _one_request_batch(n, page, start=at, n_pages=n_pages_total)
         table_full = torch.full((1, -(-T // page)), -1, dtype=torch.int32, device="cuda")
         table_full[0, :table.shape[1]] = torch.arange(n_pages_total - 1, n_pages_total - 1 - table.shape[1], -1, dtype=torch.int32)
