@@ -10,7 +10,11 @@
 //      lane scores one key; running max and sum in 32-bit; then the lanes accumulate the values, each
 //      owning dimensions lane, lane+32, ...  The walk depends only on (position, window).
 //      With a sink the running max starts at 0 and the running sum at 1: the extra term is a key
-//      of score 0 seen before all others.
+//      of score 0 seen before all others.  With a soft cap c the scaled score becomes c * tanh(score / c).
+//  (3) qkv_prepare_store: the same rows as a 32-bit product, for variants that work on whole heads in 32-bit before
+//      anything is rounded: biases added, half-split rotation, then q and k divided by their own root mean square
+//      per head (a norm without a weight), values optionally blended with the values another layer made for the
+//      same rows (v = (1 - lambda) v + lambda v_other, lambda a device scalar) and optionally saved for that use.
 #include "common.cuh"
 
 namespace imparo {
@@ -147,12 +151,101 @@ qkv_rotate_store_token_kernel(const T* __restrict__ qkv, const int* __restrict__
     }
 }
 
+
+// One warp per (token, head) of a 32-bit product row; the head passes through shared memory so that a rotation pair and
+// the head's sum of squares are at hand.  unit_eps < 0: q and k keep their length.
+template <typename T>
+__global__ void __launch_bounds__(ANY_WARPS * 32)
+qkv_prepare_store_kernel(const float* __restrict__ qkv, size_t in_width, const float* __restrict__ bias,
+                         const int* __restrict__ positions, const int* __restrict__ item_of_token,
+                         const float* __restrict__ inv_freq, int n_rot, float unit_eps,
+                         const T* __restrict__ v_other, const float* __restrict__ v_lambda, T* __restrict__ v_save,
+                         T* __restrict__ q_out, T* __restrict__ k_cache, T* __restrict__ v_cache,
+                         const int* __restrict__ table, int max_blocks, int page_size, int n_pages,
+                         int nh, int nkv, int hd, int vd, int* status) {
+    __shared__ float head[ANY_WARPS][ANY_MAX_HEAD];
+    pdl_trigger();
+    const int t = blockIdx.x;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int hh = blockIdx.y * ANY_WARPS + warp;
+    const int total = nh + 2 * nkv;
+    if (hh >= total) return;
+    const int pos = positions[t];
+    const bool is_q = hh < nh, is_k = !is_q && hh < nh + nkv;
+    const int kvh = is_q ? 0 : (is_k ? hh - nh : hh - nh - nkv);
+    const int n = (is_q || is_k) ? hd : vd;
+    const size_t col = is_q ? (size_t)hh * hd : (size_t)nh * hd + (is_k ? (size_t)kvh * hd : (size_t)nkv * hd + (size_t)kvh * vd);
+    T* dst = nullptr;
+    int bad_page = 0;
+    if (is_q) {
+        dst = q_out + ((size_t)t * nh + hh) * hd;
+    } else {
+        const int blk = pos / page_size;
+        int page = -1;
+        if (blk < max_blocks) page = table[(size_t)item_of_token[t] * max_blocks + blk];
+        if (page < 0 || page >= n_pages) {
+            bad_page = page;
+        } else {
+            const size_t r = (size_t)page * page_size + (pos % page_size);
+            dst = is_k ? k_cache + r * ((size_t)nkv * hd) + (size_t)kvh * hd : v_cache + r * ((size_t)nkv * vd) + (size_t)kvh * vd;
+        }
+    }
+    pdl_wait();
+    if (dst == nullptr) {
+        if (lane == 0) report(status, IMPARO_ST_PAGE_RANGE, 43, t, bad_page);
+        return;
+    }
+    const float* src = qkv + (size_t)t * in_width + col;
+    float* hv = head[warp];
+    for (int d = lane; d < n; d += 32) hv[d] = src[d] + (bias ? bias[col + d] : 0.f);
+    __syncwarp();
+    if (!is_q && !is_k) {                                           // a value head
+        const size_t at = (size_t)t * nkv * vd + (size_t)kvh * vd;
+        const float lam = (v_other && v_lambda) ? *v_lambda : 0.f;
+        for (int d = lane; d < n; d += 32) {
+            float v = hv[d];
+            if (v_save) v_save[at + d] = from_f32<T>(v);
+            if (v_other) v = (1.0f - lam) * v + lam * to_f32(v_other[at + d]);
+            dst[d] = from_f32<T>(v);
+        }
+        return;
+    }
+    const int half = inv_freq ? (n_rot >> 1) : 0;
+    float ss = 0.f;
+    constexpr int PER = ANY_MAX_HEAD / 32;
+    float val[PER];
+#pragma unroll
+    for (int i = 0; i < PER; ++i) {
+        const int d = lane + 32 * i;
+        float v = 0.f;
+        if (d < n) {
+            v = hv[d];
+            if (d < 2 * half) {
+                const int pair = d < half ? d : d - half;
+                float sn, cs;
+                sincosf((float)pos * inv_freq[pair], &sn, &cs);
+                v = d < half ? hv[d] * cs - hv[d + half] * sn : hv[d] * cs + hv[d - half] * sn;
+            }
+        }
+        val[i] = v;
+        ss += v * v;
+    }
+    float scale = 1.0f;
+    if (unit_eps >= 0.f) scale = 1.0f / sqrtf(warp_sum(ss) / (float)n + unit_eps);
+#pragma unroll
+    for (int i = 0; i < PER; ++i) {
+        const int d = lane + 32 * i;
+        if (d < n) dst[d] = from_f32<T>(val[i] * scale);
+    }
+}
+
 template <typename T>
 __global__ void __launch_bounds__(ANY_WARPS * 32)
 attention_any_kernel(const T* __restrict__ q, const T* __restrict__ k_cache, const T* __restrict__ v_cache,
                      const int* __restrict__ positions, const int* __restrict__ item_of_token,
                      const int* __restrict__ table, int max_blocks, int page_size, int n_pages,
-                     int window, float scale, int sink, T* __restrict__ out, int nh, int nkv, int hd, int vd, int* status) {
+                     int window, float scale, int sink, float softcap, T* __restrict__ out, int nh, int nkv, int hd, int vd,
+                     int* status) {
     __shared__ float qbuf[ANY_WARPS][ANY_MAX_HEAD];
     pdl_trigger();
     pdl_wait();
@@ -191,6 +284,7 @@ attention_any_kernel(const T* __restrict__ q, const T* __restrict__ k_cache, con
                 float d = 0.f;
                 for (int c = 0; c < hd; ++c) d += to_f32(kp[c]) * qs[c];
                 s = d * scale;
+                if (softcap > 0.f) s = softcap * tanhf(s / softcap);
             }
         }
         const float m_new = fmaxf(m, warp_max(s));
@@ -274,7 +368,7 @@ extern "C" int imparo_qkv_rotate_store(const void* qkv, int dtype, const int* po
 extern "C" int imparo_attention_any(const void* q, const void* k_cache, const void* v_cache, int dtype,
                                     const int* positions, const int* item_of_token,
                                     const int* table, int max_blocks, int page_size, int n_pages,
-                                    int window, float scale, int sink, void* out,
+                                    int window, float scale, int sink, float softcap, void* out,
                                     int n_tok, int nh, int nkv, int hd, int vd, int* status, cudaStream_t stream) {
     if (n_tok <= 0) return 0;
     if (hd < 1 || hd > ANY_MAX_HEAD || vd < 1 || vd > ANY_MAX_HEAD) return -3;
@@ -283,12 +377,39 @@ extern "C" int imparo_attention_any(const void* q, const void* k_cache, const vo
     if (dtype == IMPARO_DT_F32)
         launch(attention_any_kernel<float>, grid, dim3(ANY_WARPS * 32), 0, stream,
                (const float*)q, (const float*)k_cache, (const float*)v_cache, positions, item_of_token, table,
-               max_blocks, page_size, n_pages, window, scale, sink, (float*)out, nh, nkv, hd, vd, status);
+               max_blocks, page_size, n_pages, window, scale, sink, softcap, (float*)out, nh, nkv, hd, vd, status);
     else if (dtype == IMPARO_DT_BF16)
         launch(attention_any_kernel<__nv_bfloat16>, grid, dim3(ANY_WARPS * 32), 0, stream,
                (const __nv_bfloat16*)q, (const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache, positions,
-               item_of_token, table, max_blocks, page_size, n_pages, window, scale, sink, (__nv_bfloat16*)out, nh, nkv, hd, vd,
-               status);
+               item_of_token, table, max_blocks, page_size, n_pages, window, scale, sink, softcap, (__nv_bfloat16*)out, nh, nkv, hd,
+               vd, status);
+    else return -1;
+    IMPARO_CHECK_LAUNCH();
+    return 0;
+}
+
+// qkv: float32 [n_tok, nh*hd + nkv*hd + nkv*vd] in rows of row_stride floats; bias float32 over the same columns or null;
+// unit_eps < 0: no unit norm; v_other / v_save: [n_tok, nkv*vd] in dtype or null; v_lambda: a float on the device.
+extern "C" int imparo_qkv_prepare_store(const float* qkv, long long row_stride, const float* bias, int dtype, const int* positions,
+                                        const int* item_of_token, const float* inv_freq, int n_rot, float unit_eps,
+                                        const void* v_other, const float* v_lambda, void* v_save,
+                                        void* q_out, void* k_cache, void* v_cache, const int* table, int max_blocks,
+                                        int page_size, int n_pages, int n_tok, int nh, int nkv, int hd, int vd, int* status,
+                                        cudaStream_t stream) {
+    if (n_tok <= 0) return 0;
+    if (hd < 1 || hd > ANY_MAX_HEAD || vd < 1 || vd > ANY_MAX_HEAD) return -3;
+    if (n_rot < 0 || n_rot > hd || (n_rot & 1)) return -4;
+    if (row_stride < (long long)(nh + nkv) * hd + (long long)nkv * vd) return -2;
+    dim3 grid(n_tok, (nh + 2 * nkv + ANY_WARPS - 1) / ANY_WARPS);
+    if (dtype == IMPARO_DT_F32)
+        launch(qkv_prepare_store_kernel<float>, grid, dim3(ANY_WARPS * 32), 0, stream, qkv, (size_t)row_stride, bias, positions,
+               item_of_token, inv_freq, n_rot, unit_eps, (const float*)v_other, v_lambda, (float*)v_save, (float*)q_out,
+               (float*)k_cache, (float*)v_cache, table, max_blocks, page_size, n_pages, nh, nkv, hd, vd, status);
+    else if (dtype == IMPARO_DT_BF16)
+        launch(qkv_prepare_store_kernel<__nv_bfloat16>, grid, dim3(ANY_WARPS * 32), 0, stream, qkv, (size_t)row_stride, bias, positions,
+               item_of_token, inv_freq, n_rot, unit_eps, (const __nv_bfloat16*)v_other, v_lambda, (__nv_bfloat16*)v_save,
+               (__nv_bfloat16*)q_out, (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, table, max_blocks, page_size, n_pages, nh, nkv,
+               hd, vd, status);
     else return -1;
     IMPARO_CHECK_LAUNCH();
     return 0;

@@ -1,0 +1,416 @@
+// The selective state-space mixer (Mamba-2 form) over ragged batches, state in the request's slot.
+//
+// One projection row holds [z: inner | x: inner | B: groups*N | C: groups*N | dt: heads], inner = heads * vdim.
+//  (1) mamba2_conv: causal convolution per channel over [x | B | C] with a bias, then silu; inputs before a
+//      portion's first row come from the slot's conv state (the last taps-1 inputs, oldest first), zeros for a
+//      fresh request (the slot is cleared).  The same launch makes the step sizes dt = softplus(dt + dt_bias) in
+//      32-bit.  A second small kernel then moves the conv state on (it runs after every reader of the old state).
+//  (2) mamba2_scan: per request, head and 32 value columns one warp walks the rows in order with the state column
+//      S[:, p] in registers:  S = exp(-exp(A_log) dt) S + dt B x[p];  y[p] = C . S + D x[p].  Decays, step sizes
+//      and the state are 32-bit in both precisions.
+//  (3) Long portions run in chunks of L rows side by side (three launches, as the decayed linear attention does):
+//      every chunk's own state from zero and its total decay; a scan over each request's chunks that leaves every
+//      chunk's starting state and the request's new state; every chunk's outputs from its starting state plus the
+//      rows inside the chunk.  32-bit on CUDA cores.
+//  (4) gate_group_rmsnorm: y * silu(z), then an RMS norm over each of `groups` equal stretches of the row, times a
+//      weight.
+#include "common.cuh"
+
+namespace imparo {
+
+__device__ __forceinline__ float softplus_f(float z) { return z > 20.f ? z : log1pf(expf(z)); }
+
+// ---- (1) convolution + step sizes ------------------------------------------------------------------------------
+template <typename T>
+__global__ void __launch_bounds__(256)
+mamba2_conv_kernel(const T* __restrict__ proj, size_t stride, int x_off, int dt_off, int channels, int heads, int taps,
+                   const float* __restrict__ w, const float* __restrict__ bias, const float* __restrict__ dt_bias,
+                   const float* __restrict__ state, const int* __restrict__ item_row_start,
+                   const int* __restrict__ item_of_token, const int* __restrict__ item_slot, int n_slots,
+                   float* __restrict__ xbc, float* __restrict__ dt, int* status) {
+    pdl_trigger();
+    const int t = blockIdx.x;
+    const int c = blockIdx.y * blockDim.x + threadIdx.x;
+    const int item = item_of_token[t];
+    const int first = item_row_start[item];
+    const int slot = item_slot[item];
+    pdl_wait();
+    if (c >= channels + heads) return;
+    if (c >= channels) {                                          // a step size
+        const int h = c - channels;
+        dt[(size_t)t * heads + h] = softplus_f(to_f32(proj[(size_t)t * stride + dt_off + h]) + dt_bias[h]);
+        return;
+    }
+    if (slot < 0 || slot >= n_slots) {
+        if (c == 0) report(status, IMPARO_ST_SLOT_RANGE, 61, t, slot);
+        return;
+    }
+    const float* st = state + (size_t)slot * (taps - 1) * channels;
+    float acc = bias ? bias[c] : 0.f;
+    const int j = t - first;                                      // row within the portion
+    for (int k = 0; k < taps; ++k) {
+        const int src = j - (taps - 1 - k);
+        const float u = src >= 0 ? to_f32(proj[(size_t)(first + src) * stride + x_off + c])
+                                 : st[(size_t)(taps - 1 + src) * channels + c];
+        acc += w[(size_t)c * taps + k] * u;
+    }
+    xbc[(size_t)t * channels + c] = silu(acc);
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256)
+mamba2_conv_state_kernel(const T* __restrict__ proj, size_t stride, int x_off, int channels, int taps,
+                         float* __restrict__ state, const int* __restrict__ item_row_start,
+                         const int* __restrict__ item_slot, int n_slots) {
+    pdl_trigger();
+    const int item = blockIdx.x;
+    const int c = blockIdx.y * blockDim.x + threadIdx.x;
+    const int first = item_row_start[item], n = item_row_start[item + 1] - first;
+    const int slot = item_slot[item];
+    pdl_wait();
+    if (c >= channels || slot < 0 || slot >= n_slots) return;
+    float* st = state + (size_t)slot * (taps - 1) * channels;
+    const int keep = taps - 1;
+    // entry i of the new state is input number (n - keep + i) of the portion; negative numbers are old entries
+    float moved[16];
+    for (int i = 0; i < keep; ++i) {
+        const int src = n - keep + i;
+        moved[i] = src >= 0 ? to_f32(proj[(size_t)(first + src) * stride + x_off + c]) : st[(size_t)(keep + src) * channels + c];
+    }
+    for (int i = 0; i < keep; ++i) st[(size_t)i * channels + c] = moved[i];
+}
+
+// ---- (2) the recurrence, row by row ------------------------------------------------------------------------------
+// grid (heads, items, ceil(vdim / 32)), one warp each
+template <int NMAX>
+__global__ void __launch_bounds__(32)
+mamba2_scan_kernel(const float* __restrict__ xbc, const float* __restrict__ dt, const float* __restrict__ A_log,
+                   const float* __restrict__ D, float* __restrict__ state, const int* __restrict__ item_row_start,
+                   const int* __restrict__ item_slot, int n_slots, float* __restrict__ y,
+                   int heads, int vdim, int N, int groups, int* status) {
+    __shared__ float bc[2][NMAX];
+    pdl_trigger();
+    const int h = blockIdx.x, item = blockIdx.y, lane = threadIdx.x;
+    const int p = blockIdx.z * 32 + lane;
+    const int first = item_row_start[item], last = item_row_start[item + 1];
+    const int slot = item_slot[item];
+    const float a = -expf(A_log[h]);
+    const float d_skip = D[h];
+    pdl_wait();
+    if (slot < 0 || slot >= n_slots) {
+        if (lane == 0 && blockIdx.z == 0 && h == 0) report(status, IMPARO_ST_SLOT_RANGE, 62, item, slot);
+        return;
+    }
+    const int inner = heads * vdim, channels = inner + 2 * groups * N;
+    const int g = h / (heads / groups);
+    const bool live = p < vdim;
+    float* sp = state + (((size_t)slot * heads + h) * N) * vdim + p;
+    float S[NMAX];
+#pragma unroll
+    for (int n = 0; n < NMAX; ++n) S[n] = (live && n < N) ? sp[(size_t)n * vdim] : 0.f;
+    for (int t = first; t < last; ++t) {
+        const float* row = xbc + (size_t)t * channels;
+        __syncwarp();
+        for (int n = lane; n < N; n += 32) {
+            bc[0][n] = row[inner + g * N + n];
+            bc[1][n] = row[inner + groups * N + g * N + n];
+        }
+        __syncwarp();
+        const float step = dt[(size_t)t * heads + h];
+        const float decay = expf(a * step);
+        const float xv = live ? row[h * vdim + p] : 0.f;
+        const float dx = step * xv;
+        float acc = 0.f;
+#pragma unroll
+        for (int n = 0; n < NMAX; ++n) {
+            if (n < N) {
+                S[n] = decay * S[n] + bc[0][n] * dx;
+                acc += S[n] * bc[1][n];
+            }
+        }
+        if (live) y[(size_t)t * inner + h * vdim + p] = acc + d_skip * xv;
+    }
+    if (live) {
+#pragma unroll
+        for (int n = 0; n < NMAX; ++n)
+            if (n < N) sp[(size_t)n * vdim] = S[n];
+    }
+}
+
+// ---- (3) long portions in chunks -----------------------------------------------------------------------------------
+// Chunk c of the launch covers rows [lo, hi) of one request (chunks never straddle requests): chunk_item[c],
+// chunk_lo[c], chunk_hi[c] are made by a small kernel from item_row_start.  Unused chunks have lo == hi.
+__global__ void mamba2_chunk_plan_kernel(const int* __restrict__ item_row_start, int n_items, int L, int max_chunks,
+                                         int* __restrict__ chunk_item, int* __restrict__ chunk_lo, int* __restrict__ chunk_hi,
+                                         int* __restrict__ item_chunk_start) {
+    pdl_trigger();
+    pdl_wait();
+    if (threadIdx.x != 0 || blockIdx.x != 0) return;
+    int c = 0;
+    for (int i = 0; i < n_items; ++i) {
+        item_chunk_start[i] = c;
+        for (int lo = item_row_start[i]; lo < item_row_start[i + 1] && c < max_chunks; lo += L) {
+            chunk_item[c] = i; chunk_lo[c] = lo; chunk_hi[c] = min(lo + L, item_row_start[i + 1]);
+            ++c;
+        }
+    }
+    item_chunk_start[n_items] = c;
+    for (; c < max_chunks; ++c) { chunk_item[c] = -1; chunk_lo[c] = 0; chunk_hi[c] = 0; }
+}
+
+// every chunk's own state from zero [chunk, heads, N, vdim] and the chunk's total decay [chunk, heads]
+template <int NMAX>
+__global__ void __launch_bounds__(32)
+mamba2_chunk_state_kernel(const float* __restrict__ xbc, const float* __restrict__ dt, const float* __restrict__ A_log,
+                          const int* __restrict__ chunk_lo, const int* __restrict__ chunk_hi,
+                          float* __restrict__ chunk_state, float* __restrict__ chunk_decay,
+                          int heads, int vdim, int N, int groups) {
+    __shared__ float bs[NMAX];
+    pdl_trigger();
+    const int h = blockIdx.x, c = blockIdx.y, lane = threadIdx.x;
+    const int p = blockIdx.z * 32 + lane;
+    const float a = -expf(A_log[h]);
+    pdl_wait();
+    const int lo = chunk_lo[c], hi = chunk_hi[c];
+    if (lo >= hi) return;
+    const int inner = heads * vdim, channels = inner + 2 * groups * N;
+    const int g = h / (heads / groups);
+    const bool live = p < vdim;
+    float S[NMAX];
+#pragma unroll
+    for (int n = 0; n < NMAX; ++n) S[n] = 0.f;
+    float total = 0.f;                                            // sum of a * dt over the chunk
+    for (int t = lo; t < hi; ++t) {
+        const float* row = xbc + (size_t)t * channels;
+        __syncwarp();
+        for (int n = lane; n < N; n += 32) bs[n] = row[inner + g * N + n];
+        __syncwarp();
+        const float step = dt[(size_t)t * heads + h];
+        const float decay = expf(a * step);
+        total += a * step;
+        const float dx = live ? step * row[h * vdim + p] : 0.f;
+#pragma unroll
+        for (int n = 0; n < NMAX; ++n)
+            if (n < N) S[n] = decay * S[n] + bs[n] * dx;
+    }
+    if (live) {
+        float* out = chunk_state + (((size_t)c * heads + h) * N) * vdim + p;
+#pragma unroll
+        for (int n = 0; n < NMAX; ++n)
+            if (n < N) out[(size_t)n * vdim] = S[n];
+    }
+    if (lane == 0 && blockIdx.z == 0) chunk_decay[(size_t)c * heads + h] = total;
+}
+
+// per request and head: chunk_state[c] becomes the state BEFORE chunk c; the slot gets the state after the last chunk
+__global__ void __launch_bounds__(256)
+mamba2_chunk_scan_kernel(float* __restrict__ chunk_state, const float* __restrict__ chunk_decay,
+                         const int* __restrict__ item_chunk_start, const int* __restrict__ item_slot, int n_slots,
+                         float* __restrict__ state, int heads, int vdim, int N, int* status) {
+    pdl_trigger();
+    const int h = blockIdx.x, item = blockIdx.y;
+    const int slot = item_slot[item];
+    pdl_wait();
+    if (slot < 0 || slot >= n_slots) {
+        if (threadIdx.x == 0 && h == 0 && blockIdx.z == 0) report(status, IMPARO_ST_SLOT_RANGE, 63, item, slot);
+        return;
+    }
+    const int c0 = item_chunk_start[item], c1 = item_chunk_start[item + 1];
+    const int per = N * vdim;
+    for (int e = blockIdx.z * blockDim.x + threadIdx.x; e < per; e += gridDim.z * blockDim.x) {
+        float* sp = state + ((size_t)slot * heads + h) * per + e;
+        float S = *sp;
+        for (int c = c0; c < c1; ++c) {
+            float* cs = chunk_state + ((size_t)c * heads + h) * per + e;
+            const float own = *cs;
+            *cs = S;
+            S = expf(chunk_decay[(size_t)c * heads + h]) * S + own;
+        }
+        *sp = S;
+    }
+}
+
+// every chunk's outputs: the recurrence inside the chunk from its starting state (chunks side by side)
+template <int NMAX>
+__global__ void __launch_bounds__(32)
+mamba2_chunk_out_kernel(const float* __restrict__ xbc, const float* __restrict__ dt, const float* __restrict__ A_log,
+                        const float* __restrict__ D, const int* __restrict__ chunk_lo, const int* __restrict__ chunk_hi,
+                        const float* __restrict__ chunk_state, float* __restrict__ y,
+                        int heads, int vdim, int N, int groups) {
+    __shared__ float bc[2][NMAX];
+    pdl_trigger();
+    const int h = blockIdx.x, c = blockIdx.y, lane = threadIdx.x;
+    const int p = blockIdx.z * 32 + lane;
+    const float a = -expf(A_log[h]);
+    const float d_skip = D[h];
+    pdl_wait();
+    const int lo = chunk_lo[c], hi = chunk_hi[c];
+    if (lo >= hi) return;
+    const int inner = heads * vdim, channels = inner + 2 * groups * N;
+    const int g = h / (heads / groups);
+    const bool live = p < vdim;
+    const float* sp = chunk_state + (((size_t)c * heads + h) * N) * vdim + p;
+    float S[NMAX];
+#pragma unroll
+    for (int n = 0; n < NMAX; ++n) S[n] = (live && n < N) ? sp[(size_t)n * vdim] : 0.f;
+    for (int t = lo; t < hi; ++t) {
+        const float* row = xbc + (size_t)t * channels;
+        __syncwarp();
+        for (int n = lane; n < N; n += 32) {
+            bc[0][n] = row[inner + g * N + n];
+            bc[1][n] = row[inner + groups * N + g * N + n];
+        }
+        __syncwarp();
+        const float step = dt[(size_t)t * heads + h];
+        const float decay = expf(a * step);
+        const float xv = live ? row[h * vdim + p] : 0.f;
+        const float dx = step * xv;
+        float acc = 0.f;
+#pragma unroll
+        for (int n = 0; n < NMAX; ++n) {
+            if (n < N) {
+                S[n] = decay * S[n] + bc[0][n] * dx;
+                acc += S[n] * bc[1][n];
+            }
+        }
+        if (live) y[(size_t)t * inner + h * vdim + p] = acc + d_skip * xv;
+    }
+}
+
+// ---- (4) gate, then a norm per stretch of the row ----------------------------------------------------------------
+// grid (rows, groups): out[r, s] = (y silu(z))[r, s] / rms over the stretch * w[s]
+template <typename T, typename TZ>
+__global__ void __launch_bounds__(256)
+gate_group_rmsnorm_kernel(const float* __restrict__ y, const TZ* __restrict__ z, size_t z_stride, const float* __restrict__ w,
+                          float eps, T* __restrict__ out, int width, int groups) {
+    __shared__ float scratch[33];
+    pdl_trigger();
+    pdl_wait();
+    const int r = blockIdx.x, grp = blockIdx.y;
+    const int per = width / groups;
+    const float* yr = y + (size_t)r * width + (size_t)grp * per;
+    const TZ* zr = z + (size_t)r * z_stride + (size_t)grp * per;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < per; i += blockDim.x) {
+        const float v = yr[i] * silu(to_f32(zr[i]));
+        ss += v * v;
+    }
+    ss = block_sum(ss, scratch);
+    const float scale = 1.0f / sqrtf(ss / (float)per + eps);
+    T* o = out + (size_t)r * width + (size_t)grp * per;
+    const float* wg = w + (size_t)grp * per;
+    for (int i = threadIdx.x; i < per; i += blockDim.x)
+        o[i] = from_f32<T>(yr[i] * silu(to_f32(zr[i])) * scale * wg[i]);
+}
+
+}  // namespace imparo
+
+using namespace imparo;
+
+// proj: [n_tok, >= dt_off + heads] rows of `stride` elements in dtype; xbc float32 [n_tok, channels]; dt float32
+// [n_tok, heads]; state float32 [n_slots, taps-1, channels].  Two launches.
+extern "C" int imparo_mamba2_conv(const void* proj, int dtype, long long stride, int x_off, int dt_off, int channels, int heads,
+                                  int taps, const float* w, const float* bias, const float* dt_bias, float* state,
+                                  const int* item_row_start, const int* item_of_token, const int* item_slot, int n_items,
+                                  int n_slots, int n_tok, float* xbc, float* dt, int* status, cudaStream_t stream) {
+    if (n_tok <= 0) return 0;
+    if (taps < 1 || taps > 17) return -6;
+    dim3 grid(n_tok, (channels + heads + 255) / 256), sgrid(n_items, (channels + 255) / 256);
+    if (dtype == IMPARO_DT_F32) {
+        launch(mamba2_conv_kernel<float>, grid, dim3(256), 0, stream, (const float*)proj, (size_t)stride, x_off, dt_off, channels, heads,
+               taps, w, bias, dt_bias, (const float*)state, item_row_start, item_of_token, item_slot, n_slots, xbc, dt, status);
+        IMPARO_CHECK_LAUNCH();
+        if (taps > 1)
+            launch(mamba2_conv_state_kernel<float>, sgrid, dim3(256), 0, stream, (const float*)proj, (size_t)stride, x_off, channels, taps,
+                   state, item_row_start, item_slot, n_slots);
+    } else if (dtype == IMPARO_DT_BF16) {
+        launch(mamba2_conv_kernel<__nv_bfloat16>, grid, dim3(256), 0, stream, (const __nv_bfloat16*)proj, (size_t)stride, x_off, dt_off,
+               channels, heads, taps, w, bias, dt_bias, (const float*)state, item_row_start, item_of_token, item_slot, n_slots, xbc, dt,
+               status);
+        IMPARO_CHECK_LAUNCH();
+        if (taps > 1)
+            launch(mamba2_conv_state_kernel<__nv_bfloat16>, sgrid, dim3(256), 0, stream, (const __nv_bfloat16*)proj, (size_t)stride, x_off,
+                   channels, taps, state, item_row_start, item_slot, n_slots);
+    } else return -1;
+    IMPARO_CHECK_LAUNCH();
+    return 0;
+}
+
+#define MAMBA2_BY_N(CALL)                                       \
+    do {                                                        \
+        if (N <= 16) { CALL(16); }                              \
+        else if (N <= 32) { CALL(32); }                         \
+        else if (N <= 64) { CALL(64); }                         \
+        else if (N <= 128) { CALL(128); }                       \
+        else { CALL(256); }                                     \
+    } while (0)
+
+extern "C" int imparo_mamba2_scan(const float* xbc, const float* dt, const float* A_log, const float* D, float* state,
+                                  const int* item_row_start, const int* item_slot, int n_items, int n_slots, float* y,
+                                  int heads, int vdim, int N, int groups, int* status, cudaStream_t stream) {
+    if (n_items <= 0) return 0;
+    if (N < 1 || N > 256) return -3;
+    if (groups < 1 || heads % groups) return -5;
+    dim3 grid(heads, n_items, (vdim + 31) / 32);
+#define CALL(NM) launch(mamba2_scan_kernel<NM>, grid, dim3(32), 0, stream, xbc, dt, A_log, D, state, item_row_start, item_slot, \
+                        n_slots, y, heads, vdim, N, groups, status)
+    MAMBA2_BY_N(CALL);
+#undef CALL
+    IMPARO_CHECK_LAUNCH();
+    return 0;
+}
+
+// scratch_i: int32 [3 * max_chunks + n_items + 1]; chunk_state float32 [max_chunks, heads, N, vdim]; chunk_decay float32
+// [max_chunks, heads]; max_chunks >= n_tok / L + n_items.  Four launches.
+extern "C" int imparo_mamba2_scan_chunked(const float* xbc, const float* dt, const float* A_log, const float* D, float* state,
+                                          const int* item_row_start, const int* item_slot, int n_items, int n_slots, float* y,
+                                          int heads, int vdim, int N, int groups, int L, int max_chunks, int* scratch_i,
+                                          float* chunk_state, float* chunk_decay, int* status, cudaStream_t stream) {
+    if (n_items <= 0) return 0;
+    if (N < 1 || N > 256) return -3;
+    if (groups < 1 || heads % groups) return -5;
+    if (L < 1 || max_chunks < 1) return -2;
+    int* chunk_item = scratch_i;
+    int* chunk_lo = scratch_i + max_chunks;
+    int* chunk_hi = scratch_i + 2 * max_chunks;
+    int* item_chunk_start = scratch_i + 3 * max_chunks;
+    launch(mamba2_chunk_plan_kernel, dim3(1), dim3(32), 0, stream, item_row_start, n_items, L, max_chunks, chunk_item, chunk_lo,
+           chunk_hi, item_chunk_start);
+    IMPARO_CHECK_LAUNCH();
+    dim3 grid(heads, max_chunks, (vdim + 31) / 32);
+#define CALL(NM) launch(mamba2_chunk_state_kernel<NM>, grid, dim3(32), 0, stream, xbc, dt, A_log, (const int*)chunk_lo, \
+                        (const int*)chunk_hi, chunk_state, chunk_decay, heads, vdim, N, groups)
+    MAMBA2_BY_N(CALL);
+#undef CALL
+    IMPARO_CHECK_LAUNCH();
+    const int per = N * vdim;
+    launch(mamba2_chunk_scan_kernel, dim3(heads, n_items, (per + 255) / 256), dim3(256), 0, stream, chunk_state,
+           (const float*)chunk_decay, (const int*)item_chunk_start, item_slot, n_slots, state, heads, vdim, N, status);
+    IMPARO_CHECK_LAUNCH();
+#define CALL(NM) launch(mamba2_chunk_out_kernel<NM>, grid, dim3(32), 0, stream, xbc, dt, A_log, D, (const int*)chunk_lo, \
+                        (const int*)chunk_hi, (const float*)chunk_state, y, heads, vdim, N, groups)
+    MAMBA2_BY_N(CALL);
+#undef CALL
+    IMPARO_CHECK_LAUNCH();
+    return 0;
+}
+
+// y float32 [rows, width]; z [rows, width] in rows of z_stride elements (z_dtype); out [rows, width] in out_dtype
+extern "C" int imparo_gate_group_rmsnorm(const float* y, const void* z, int z_dtype, long long z_stride, const float* w, float eps,
+                                         void* out, int out_dtype, int rows, int width, int groups, cudaStream_t stream) {
+    if (rows <= 0) return 0;
+    if (groups < 1 || width % groups) return -2;
+    dim3 grid(rows, groups);
+    if (z_dtype == IMPARO_DT_F32 && out_dtype == IMPARO_DT_F32)
+        launch(gate_group_rmsnorm_kernel<float, float>, grid, dim3(256), 0, stream, y, (const float*)z, (size_t)z_stride, w, eps,
+               (float*)out, width, groups);
+    else if (z_dtype == IMPARO_DT_BF16 && out_dtype == IMPARO_DT_BF16)
+        launch(gate_group_rmsnorm_kernel<__nv_bfloat16, __nv_bfloat16>, grid, dim3(256), 0, stream, y, (const __nv_bfloat16*)z,
+               (size_t)z_stride, w, eps, (__nv_bfloat16*)out, width, groups);
+    else if (z_dtype == IMPARO_DT_F32 && out_dtype == IMPARO_DT_BF16)
+        launch(gate_group_rmsnorm_kernel<__nv_bfloat16, float>, grid, dim3(256), 0, stream, y, (const float*)z, (size_t)z_stride, w, eps,
+               (__nv_bfloat16*)out, width, groups);
+    else return -1;
+    IMPARO_CHECK_LAUNCH();
+    return 0;
+}

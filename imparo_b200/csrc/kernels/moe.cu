@@ -1,0 +1,437 @@
+// A routed feed-forward (mixture of experts) over the rows of a step.
+//
+//  (1) moe_route: router logits z = W_r h in 32-bit (one warp per row), score = sigmoid(z) or softmax(z), the `top`
+//      largest scores (ties: the lower expert), optionally renormalised to sum 1.  Leaves expert ids [rows, top] and
+//      weights [rows, top].
+//  (2) moe_rows_*: each (row, choice) pair on its own: the expert's gate and up rows times the (optionally weighted)
+//      input, silu(gate) * up, then the expert's down rows; the choices of a row are added in order.  Weights are
+//      streamed once per pair: the form for steps of few rows.
+//  (3) moe_group_*: pairs sorted by expert (a counting sort whose order inside an expert is the row order, so the
+//      result does not depend on what else is in the step), tiles of 32 pairs x 64 outputs per CTA: bfloat16 on
+//      tensor cores (mma.sync through wmma fragments, 32-bit accumulation), 32-bit with FFMA.  The tile list is made
+//      on the device from the counts; CTAs beyond it leave at once, so the launch depends on (rows, top, experts)
+//      only.
+//
+// Expert e's matrices: w_gu[e] = [gate; up] ([2 ff, width]), w_down[e] ([width, ff]).  The weight multiplies the
+// expert's input (weight_input = 1) or its output (0).
+#include "common.cuh"
+#include <mma.h>
+
+namespace imparo {
+
+// ---- (1) router -------------------------------------------------------------------------------------------------
+template <typename T>
+__global__ void __launch_bounds__(128)
+moe_route_kernel(const T* __restrict__ h, const float* __restrict__ w_r, int n_rows, int width, int experts, int top,
+                 int softmax_scores, int renormalise, int* __restrict__ ids, float* __restrict__ wts) {
+    extern __shared__ float route_smem[];
+    pdl_trigger();
+    pdl_wait();
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int r = blockIdx.x * 4 + warp;
+    if (r >= n_rows) return;
+    float* s = route_smem + (size_t)warp * experts;
+    const T* hr = h + (size_t)r * width;
+    for (int e = 0; e < experts; ++e) {
+        const float* wr = w_r + (size_t)e * width;
+        float acc = 0.f;
+        for (int i = lane; i < width; i += 32) acc += wr[i] * to_f32(hr[i]);
+        acc = warp_sum(acc);
+        if (lane == 0) s[e] = acc;
+    }
+    __syncwarp();
+    if (softmax_scores) {
+        float m = -INFINITY;
+        for (int e = lane; e < experts; e += 32) m = fmaxf(m, s[e]);
+        m = warp_max(m);
+        float l = 0.f;
+        for (int e = lane; e < experts; e += 32) l += expf(s[e] - m);
+        l = warp_sum(l);
+        for (int e = lane; e < experts; e += 32) s[e] = expf(s[e] - m) / l;
+    } else {
+        for (int e = lane; e < experts; e += 32) s[e] = 1.0f / (1.0f + expf(-s[e]));
+    }
+    __syncwarp();
+    float total = 0.f;
+    for (int k = 0; k < top; ++k) {
+        float best = -INFINITY;
+        int arg = 0x7fffffff;
+        for (int e = lane; e < experts; e += 32) {
+            const float v = s[e];
+            if (v > best) { best = v; arg = e; }
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+            const int oa = __shfl_xor_sync(0xffffffffu, arg, o);
+            if (ob > best || (ob == best && oa < arg)) { best = ob; arg = oa; }
+        }
+        if (lane == 0) {
+            ids[(size_t)r * top + k] = arg;
+            wts[(size_t)r * top + k] = best;
+            s[arg] = -INFINITY;
+        }
+        total += best;
+        __syncwarp();
+    }
+    if (renormalise && lane < top) wts[(size_t)r * top + lane] /= total;
+}
+
+// ---- (2) pair by pair ---------------------------------------------------------------------------------------------
+// grid (rows * top, ceil(ff / 32)); 8 warps, each 4 features
+template <typename T>
+__global__ void __launch_bounds__(256)
+moe_rows_up_kernel(const T* __restrict__ h, const T* __restrict__ w_gu, const int* __restrict__ ids, const float* __restrict__ wts,
+                   int width, int ff, int top, int experts, int weight_input, T* __restrict__ mid) {
+    extern __shared__ float up_smem[];
+    pdl_trigger();
+    pdl_wait();
+    const int pair = blockIdx.x, r = pair / top;
+    const int e = ids[pair];
+    if (e < 0 || e >= experts) return;
+    const float wt = weight_input ? wts[pair] : 1.0f;
+    const T* hr = h + (size_t)r * width;
+    for (int i = threadIdx.x; i < width; i += blockDim.x) up_smem[i] = to_f32(from_f32<T>(wt * to_f32(hr[i])));
+    __syncthreads();
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const T* base = w_gu + (size_t)e * 2 * ff * width;
+    for (int j = 0; j < 4; ++j) {
+        const int f = blockIdx.y * 32 + warp * 4 + j;
+        if (f >= ff) break;
+        const T* g = base + (size_t)f * width;
+        const T* u = base + (size_t)(ff + f) * width;
+        float ag = 0.f, au = 0.f;
+        for (int i = lane; i < width; i += 32) {
+            const float x = up_smem[i];
+            ag += to_f32(g[i]) * x;
+            au += to_f32(u[i]) * x;
+        }
+        ag = warp_sum(ag);
+        au = warp_sum(au);
+        if (lane == 0) mid[(size_t)pair * ff + f] = from_f32<T>(silu(ag) * au);
+    }
+}
+
+// grid (rows, ceil(width / 32)); 8 warps, each 4 outputs; out float32 [rows, width] is overwritten
+template <typename T>
+__global__ void __launch_bounds__(256)
+moe_rows_down_kernel(const T* __restrict__ mid, const T* __restrict__ w_down, const int* __restrict__ ids,
+                     const float* __restrict__ wts, int width, int ff, int top, int experts, int weight_input,
+                     float* __restrict__ out) {
+    extern __shared__ float down_smem[];
+    pdl_trigger();
+    pdl_wait();
+    const int r = blockIdx.x;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    float acc[4] = {0.f, 0.f, 0.f, 0.f};
+    for (int k = 0; k < top; ++k) {
+        const int pair = r * top + k;
+        const int e = ids[pair];
+        __syncthreads();
+        for (int i = threadIdx.x; i < ff; i += blockDim.x) down_smem[i] = to_f32(mid[(size_t)pair * ff + i]);
+        __syncthreads();
+        if (e < 0 || e >= experts) continue;
+        const float wt = weight_input ? 1.0f : wts[pair];
+        for (int j = 0; j < 4; ++j) {
+            const int o = blockIdx.y * 32 + warp * 4 + j;
+            if (o >= width) break;
+            const T* d = w_down + ((size_t)e * width + o) * ff;
+            float a = 0.f;
+            for (int i = lane; i < ff; i += 32) a += to_f32(d[i]) * down_smem[i];
+            acc[j] += wt * warp_sum(a);
+        }
+    }
+    if (lane == 0)
+        for (int j = 0; j < 4; ++j) {
+            const int o = blockIdx.y * 32 + warp * 4 + j;
+            if (o < width) out[(size_t)r * width + o] = acc[j];
+        }
+}
+
+// ---- (3) grouped by expert ----------------------------------------------------------------------------------------
+constexpr int GM = 32, GN = 64, GK = 32;          // tile: pairs x outputs, K step
+
+// One block: counts per expert, offsets, the sorted pair list (stable: by expert, then by pair index) and the tile list.
+// plan: [0] number of tiles; tile_expert[t], tile_first[t] (index into sorted), tile_rows[t]
+__global__ void __launch_bounds__(1024)
+moe_group_plan_kernel(const int* __restrict__ ids, int n_pairs, int experts, int* __restrict__ sorted,
+                      int* __restrict__ expert_start, int* __restrict__ plan, int max_tiles) {
+    extern __shared__ int plan_smem[];               // experts + 1 offsets
+    pdl_trigger();
+    pdl_wait();
+    int* start = plan_smem;
+    const int tid = threadIdx.x;
+    // thread e counts its expert's pairs and then writes them in pair order: the order inside an expert is by row
+    for (int e = tid; e <= experts; e += blockDim.x) start[e] = 0;
+    __syncthreads();
+    for (int e = tid; e < experts; e += blockDim.x) {
+        int c = 0;
+        for (int i = 0; i < n_pairs; ++i) c += ids[i] == e;
+        start[e + 1] = c;
+    }
+    __syncthreads();
+    if (tid == 0) {
+        int tiles = 0;
+        for (int e = 0; e < experts; ++e) {
+            const int c = start[e + 1];
+            start[e + 1] = start[e] + c;
+            for (int lo = 0; lo < c && tiles < max_tiles; lo += GM) {
+                plan[1 + 3 * tiles] = e;
+                plan[2 + 3 * tiles] = start[e] + lo;
+                plan[3 + 3 * tiles] = min(GM, c - lo);
+                ++tiles;
+            }
+        }
+        plan[0] = tiles;
+    }
+    __syncthreads();
+    for (int e = tid; e < experts; e += blockDim.x) {
+        int at = start[e];
+        expert_start[e] = at;
+        for (int i = 0; i < n_pairs; ++i)
+            if (ids[i] == e) sorted[at++] = i;
+    }
+    if (tid == 0) expert_start[experts] = start[experts];
+}
+
+// A[m, k]: row `pair_of[m]` of the operand (times its weight when asked), B[n, k]: the expert's matrix rows.
+// bfloat16: wmma 16x16x16, 8 warps as 2 (m) x 4 (n); float32: each thread a 2 x 4 patch with FFMA.
+template <typename T> struct GroupTile;
+
+template <> struct __align__(32) GroupTile<__nv_bfloat16> {
+    using T = __nv_bfloat16;
+    static constexpr int LDS = GK + 8;
+    T a[GM][LDS];
+    T b[GN][LDS];
+    float c[GM][GN + 4];
+};
+template <> struct __align__(32) GroupTile<float> {
+    static constexpr int LDS = GK + 1;
+    float a[GM][LDS];
+    float b[GN][LDS];
+    float c[GM][GN + 4];
+};
+
+// acc tile = A (GM x K) * B^T (GN x K); result left in sm.c
+template <typename T, typename LoadA>
+__device__ __forceinline__ void group_tile_product(GroupTile<T>& sm, LoadA load_a, const T* __restrict__ bmat, int n0, int n_rows_b,
+                                                   int K, int rows) {
+    const int tid = threadIdx.x;
+    if constexpr (sizeof(T) == 2) {
+        using namespace nvcuda;
+        const int warp = tid >> 5, wm = warp >> 2, wn = warp & 3;
+        wmma::fragment<wmma::accumulator, 16, 16, 16, float> acc;
+        wmma::fill_fragment(acc, 0.f);
+        for (int k0 = 0; k0 < K; k0 += GK) {
+            __syncthreads();
+            for (int i = tid; i < GM * GK; i += 256) {
+                const int m = i / GK, k = i % GK;
+                sm.a[m][k] = (m < rows && k0 + k < K) ? load_a(m, k0 + k) : from_f32<T>(0.f);
+            }
+            for (int i = tid; i < GN * GK; i += 256) {
+                const int n = i / GK, k = i % GK;
+                sm.b[n][k] = (n0 + n < n_rows_b && k0 + k < K) ? bmat[(size_t)(n0 + n) * K + k0 + k] : from_f32<T>(0.f);
+            }
+            __syncthreads();
+#pragma unroll
+            for (int kk = 0; kk < GK; kk += 16) {
+                wmma::fragment<wmma::matrix_a, 16, 16, 16, __nv_bfloat16, wmma::row_major> fa;
+                wmma::fragment<wmma::matrix_b, 16, 16, 16, __nv_bfloat16, wmma::col_major> fb;
+                wmma::load_matrix_sync(fa, &sm.a[wm * 16][kk], GroupTile<T>::LDS);
+                wmma::load_matrix_sync(fb, &sm.b[wn * 16][kk], GroupTile<T>::LDS);
+                wmma::mma_sync(acc, fa, fb, acc);
+            }
+        }
+        wmma::store_matrix_sync(&sm.c[wm * 16][wn * 16], acc, GN + 4, wmma::mem_row_major);
+        __syncthreads();
+    } else {
+        const int tm = (tid >> 4) * 2, tn = (tid & 15) * 4;      // 16 x 16 threads, 2 x 4 each
+        float acc[2][4] = {};
+        for (int k0 = 0; k0 < K; k0 += GK) {
+            __syncthreads();
+            for (int i = tid; i < GM * GK; i += 256) {
+                const int m = i / GK, k = i % GK;
+                sm.a[m][k] = (m < rows && k0 + k < K) ? load_a(m, k0 + k) : 0.f;
+            }
+            for (int i = tid; i < GN * GK; i += 256) {
+                const int n = i / GK, k = i % GK;
+                sm.b[n][k] = (n0 + n < n_rows_b && k0 + k < K) ? bmat[(size_t)(n0 + n) * K + k0 + k] : 0.f;
+            }
+            __syncthreads();
+            const int kn = min(GK, K - k0);
+            for (int k = 0; k < kn; ++k) {
+                float av[2], bv[4];
+#pragma unroll
+                for (int i = 0; i < 2; ++i) av[i] = sm.a[tm + i][k];
+#pragma unroll
+                for (int j = 0; j < 4; ++j) bv[j] = sm.b[tn + j][k];
+#pragma unroll
+                for (int i = 0; i < 2; ++i)
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) acc[i][j] += av[i] * bv[j];
+            }
+        }
+#pragma unroll
+        for (int i = 0; i < 2; ++i)
+#pragma unroll
+            for (int j = 0; j < 4; ++j) sm.c[tm + i][tn + j] = acc[i][j];
+        __syncthreads();
+    }
+}
+
+// grid (max_tiles, ceil(ff / 64)): mid[pair, f] = silu(gate) * up for the tile's pairs; gate and up as two products
+template <typename T>
+__global__ void __launch_bounds__(256)
+moe_group_up_kernel(const T* __restrict__ h, const T* __restrict__ w_gu, const int* __restrict__ sorted, const int* __restrict__ plan,
+                    const float* __restrict__ wts, int width, int ff, int top, int weight_input, T* __restrict__ mid) {
+    __shared__ GroupTile<T> sm;
+    __shared__ int pair_of[GM];
+    __shared__ float wt_of[GM];
+    __shared__ float gate_c[GM][GN];
+    pdl_trigger();
+    pdl_wait();
+    const int tile = blockIdx.x;
+    if (tile >= plan[0]) return;
+    const int e = plan[1 + 3 * tile], first = plan[2 + 3 * tile], rows = plan[3 + 3 * tile];
+    if (threadIdx.x < GM) {
+        const int p = threadIdx.x < rows ? sorted[first + threadIdx.x] : -1;
+        pair_of[threadIdx.x] = p;
+        wt_of[threadIdx.x] = (p >= 0 && weight_input) ? wts[p] : 1.0f;
+    }
+    __syncthreads();
+    const int n0 = blockIdx.y * GN;
+    auto load_a = [&](int m, int k) -> T {
+        return from_f32<T>(wt_of[m] * to_f32(h[(size_t)(pair_of[m] / top) * width + k]));
+    };
+    const T* base = w_gu + (size_t)e * 2 * ff * width;
+    group_tile_product<T>(sm, load_a, base, n0, ff, width, rows);
+    for (int i = threadIdx.x; i < GM * GN; i += 256) gate_c[i / GN][i % GN] = sm.c[i / GN][i % GN];
+    group_tile_product<T>(sm, load_a, base + (size_t)ff * width, n0, ff, width, rows);
+    for (int i = threadIdx.x; i < GM * GN; i += 256) {
+        const int m = i / GN, n = i % GN;
+        if (m < rows && n0 + n < ff) mid[(size_t)pair_of[m] * ff + n0 + n] = from_f32<T>(silu(gate_c[m][n]) * sm.c[m][n]);
+    }
+}
+
+// grid (max_tiles, ceil(width / 64)): pair_out[pair, o] = down row o . mid[pair]  (times the weight when it is on the output)
+template <typename T>
+__global__ void __launch_bounds__(256)
+moe_group_down_kernel(const T* __restrict__ mid, const T* __restrict__ w_down, const int* __restrict__ sorted,
+                      const int* __restrict__ plan, const float* __restrict__ wts, int width, int ff, int weight_input,
+                      float* __restrict__ pair_out) {
+    __shared__ GroupTile<T> sm;
+    __shared__ int pair_of[GM];
+    pdl_trigger();
+    pdl_wait();
+    const int tile = blockIdx.x;
+    if (tile >= plan[0]) return;
+    const int e = plan[1 + 3 * tile], first = plan[2 + 3 * tile], rows = plan[3 + 3 * tile];
+    if (threadIdx.x < GM) pair_of[threadIdx.x] = threadIdx.x < rows ? sorted[first + threadIdx.x] : -1;
+    __syncthreads();
+    const int n0 = blockIdx.y * GN;
+    auto load_a = [&](int m, int k) -> T { return mid[(size_t)pair_of[m] * ff + k]; };
+    group_tile_product<T>(sm, load_a, w_down + (size_t)e * width * ff, n0, width, ff, rows);
+    for (int i = threadIdx.x; i < GM * GN; i += 256) {
+        const int m = i / GN, n = i % GN;
+        if (m < rows && n0 + n < width) {
+            const float wt = weight_input ? 1.0f : wts[pair_of[m]];
+            pair_out[(size_t)pair_of[m] * width + n0 + n] = wt * sm.c[m][n];
+        }
+    }
+}
+
+// out[r, :] = sum over the row's choices, in order
+__global__ void __launch_bounds__(256)
+moe_sum_pairs_kernel(const float* __restrict__ pair_out, int n_rows, int width, int top, float* __restrict__ out) {
+    pdl_trigger();
+    pdl_wait();
+    const size_t total = (size_t)n_rows * width;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+        const size_t r = i / width, c = i - r * width;
+        float a = 0.f;
+        for (int k = 0; k < top; ++k) a += pair_out[(r * top + k) * width + c];
+        out[i] = a;
+    }
+}
+
+}  // namespace imparo
+
+using namespace imparo;
+
+extern "C" int imparo_moe_route(const void* h, int dtype, const float* w_r, int n_rows, int width, int experts, int top,
+                                int softmax_scores, int renormalise, int* ids, float* wts, cudaStream_t stream) {
+    if (n_rows <= 0) return 0;
+    if (top < 1 || top > experts || top > 32 || experts > 2048) return -2;
+    const size_t smem = (size_t)4 * experts * sizeof(float);
+    dim3 grid((n_rows + 3) / 4);
+    if (dtype == IMPARO_DT_F32)
+        launch(moe_route_kernel<float>, grid, dim3(128), smem, stream, (const float*)h, w_r, n_rows, width, experts, top,
+               softmax_scores, renormalise, ids, wts);
+    else if (dtype == IMPARO_DT_BF16)
+        launch(moe_route_kernel<__nv_bfloat16>, grid, dim3(128), smem, stream, (const __nv_bfloat16*)h, w_r, n_rows, width, experts,
+               top, softmax_scores, renormalise, ids, wts);
+    else return -1;
+    IMPARO_CHECK_LAUNCH();
+    return 0;
+}
+
+// mid: [n_rows * top, ff] in dtype; out float32 [n_rows, width].  Two launches.
+extern "C" int imparo_moe_rows(const void* h, const void* w_gu, const void* w_down, int dtype, const int* ids, const float* wts,
+                               int n_rows, int width, int ff, int top, int experts, int weight_input, void* mid, float* out,
+                               cudaStream_t stream) {
+    if (n_rows <= 0) return 0;
+    if ((size_t)width * 4 > 48 * 1024 || (size_t)ff * 4 > 48 * 1024) return -25;
+    dim3 g1(n_rows * top, (ff + 31) / 32), g2(n_rows, (width + 31) / 32);
+    if (dtype == IMPARO_DT_F32) {
+        launch(moe_rows_up_kernel<float>, g1, dim3(256), (size_t)width * 4, stream, (const float*)h, (const float*)w_gu, ids, wts, width,
+               ff, top, experts, weight_input, (float*)mid);
+        IMPARO_CHECK_LAUNCH();
+        launch(moe_rows_down_kernel<float>, g2, dim3(256), (size_t)ff * 4, stream, (const float*)mid, (const float*)w_down, ids, wts,
+               width, ff, top, experts, weight_input, out);
+    } else if (dtype == IMPARO_DT_BF16) {
+        launch(moe_rows_up_kernel<__nv_bfloat16>, g1, dim3(256), (size_t)width * 4, stream, (const __nv_bfloat16*)h,
+               (const __nv_bfloat16*)w_gu, ids, wts, width, ff, top, experts, weight_input, (__nv_bfloat16*)mid);
+        IMPARO_CHECK_LAUNCH();
+        launch(moe_rows_down_kernel<__nv_bfloat16>, g2, dim3(256), (size_t)ff * 4, stream, (const __nv_bfloat16*)mid,
+               (const __nv_bfloat16*)w_down, ids, wts, width, ff, top, experts, weight_input, out);
+    } else return -1;
+    IMPARO_CHECK_LAUNCH();
+    return 0;
+}
+
+// scratch_i: int32 [n_pairs + experts + 1 + 1 + 3 * max_tiles], max_tiles = n_pairs / 32 + experts; pair_out float32
+// [n_pairs, width]; mid [n_pairs, ff] in dtype; out float32 [n_rows, width].  Four launches.
+extern "C" int imparo_moe_grouped(const void* h, const void* w_gu, const void* w_down, int dtype, const int* ids, const float* wts,
+                                  int n_rows, int width, int ff, int top, int experts, int weight_input, void* mid,
+                                  float* pair_out, int* scratch_i, float* out, cudaStream_t stream) {
+    if (n_rows <= 0) return 0;
+    const int n_pairs = n_rows * top;
+    const int max_tiles = n_pairs / GM + experts;
+    if (experts > 4096) return -25;
+    int* sorted = scratch_i;
+    int* expert_start = scratch_i + n_pairs;
+    int* plan = expert_start + experts + 1;
+    launch(moe_group_plan_kernel, dim3(1), dim3(1024), (size_t)(experts + 1) * sizeof(int), stream, ids, n_pairs, experts, sorted,
+           expert_start, plan, max_tiles);
+    IMPARO_CHECK_LAUNCH();
+    dim3 g1(max_tiles, (ff + GN - 1) / GN), g2(max_tiles, (width + GN - 1) / GN);
+    if (dtype == IMPARO_DT_F32) {
+        launch(moe_group_up_kernel<float>, g1, dim3(256), 0, stream, (const float*)h, (const float*)w_gu, (const int*)sorted,
+               (const int*)plan, wts, width, ff, top, weight_input, (float*)mid);
+        IMPARO_CHECK_LAUNCH();
+        launch(moe_group_down_kernel<float>, g2, dim3(256), 0, stream, (const float*)mid, (const float*)w_down, (const int*)sorted,
+               (const int*)plan, wts, width, ff, weight_input, pair_out);
+    } else if (dtype == IMPARO_DT_BF16) {
+        launch(moe_group_up_kernel<__nv_bfloat16>, g1, dim3(256), 0, stream, (const __nv_bfloat16*)h, (const __nv_bfloat16*)w_gu,
+               (const int*)sorted, (const int*)plan, wts, width, ff, top, weight_input, (__nv_bfloat16*)mid);
+        IMPARO_CHECK_LAUNCH();
+        launch(moe_group_down_kernel<__nv_bfloat16>, g2, dim3(256), 0, stream, (const __nv_bfloat16*)mid, (const __nv_bfloat16*)w_down,
+               (const int*)sorted, (const int*)plan, wts, width, ff, weight_input, pair_out);
+    } else return -1;
+    IMPARO_CHECK_LAUNCH();
+    const size_t total = (size_t)n_rows * width;
+    launch(moe_sum_pairs_kernel, dim3((unsigned)((total + 255) / 256 > 4096 ? 4096 : (total + 255) / 256)), dim3(256), 0, stream,
+           (const float*)pair_out, n_rows, width, top, out);
+    IMPARO_CHECK_LAUNCH();
+    return 0;
+}

@@ -285,7 +285,46 @@ __global__ void softcap_kernel(float* __restrict__ x, size_t n, float cap) {
         x[i] = cap * tanhf(x[i] * inv);
 }
 
+// x[r, :] += y[r, :] / rms(y[r, :]) * w  (a norm on a sublayer's OUTPUT, then the residual add); when `copy` is given,
+// the updated row is also stored there in the activation dtype, which is what the next sublayer's products read.
+template <typename TOut>
+__global__ void __launch_bounds__(256)
+out_norm_add_kernel(float* __restrict__ x, const float* __restrict__ y, const float* __restrict__ w, float eps, int width,
+                    TOut* __restrict__ copy) {
+    __shared__ float scratch[33];
+    pdl_trigger();
+    pdl_wait();
+    const int r = blockIdx.x;
+    const float* yr = y + (size_t)r * width;
+    float* xr = x + (size_t)r * width;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < width; i += blockDim.x) { const float v = yr[i]; ss += v * v; }
+    ss = block_sum(ss, scratch);
+    const float scale = 1.0f / sqrtf(ss / (float)width + eps);
+    for (int i = threadIdx.x; i < width; i += blockDim.x) {
+        const float v = xr[i] + yr[i] * scale * w[i];
+        xr[i] = v;
+        if (copy) copy[(size_t)r * width + i] = from_f32<TOut>(v);
+    }
+}
+
+// out[i] = x[i] in another dtype
+template <typename TOut>
+__global__ void cast_rows_kernel(const float* __restrict__ x, TOut* __restrict__ out, size_t n) {
+    pdl_trigger();
+    pdl_wait();
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x)
+        out[i] = from_f32<TOut>(x[i]);
+}
+
+__global__ void scale_rows_kernel(float* x, size_t n, float factor) {
+    pdl_trigger();
+    pdl_wait();
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) x[i] *= factor;
+}
+
 }  // namespace imparo
+
 
 using namespace imparo;
 
@@ -409,6 +448,39 @@ extern "C" int imparo_softcap(float* x, long long n, float cap, cudaStream_t str
     if (n <= 0) return 0;
     if (!(cap > 0.f)) return -2;
     launch(softcap_kernel, dim3(flat_grid(n)), dim3(256), 0, stream, x, (size_t)n, cap);
+    IMPARO_CHECK_LAUNCH();
+    return 0;
+}
+
+// x float32 [rows, width] += rms-normed y * w; copy (or null): [rows, width] in copy_dtype, the updated rows
+extern "C" int imparo_out_norm_add(float* x, const float* y, const float* w, float eps, void* copy, int copy_dtype, int rows,
+                                   int width, cudaStream_t stream) {
+    if (rows <= 0) return 0;
+    if (copy != nullptr && copy_dtype == IMPARO_DT_BF16)
+        launch(out_norm_add_kernel<__nv_bfloat16>, dim3(rows), dim3(256), 0, stream, x, y, w, eps, width, (__nv_bfloat16*)copy);
+    else if (copy == nullptr || copy_dtype == IMPARO_DT_F32)
+        launch(out_norm_add_kernel<float>, dim3(rows), dim3(256), 0, stream, x, y, w, eps, width, (float*)copy);
+    else return -1;
+    IMPARO_CHECK_LAUNCH();
+    return 0;
+}
+
+extern "C" int imparo_cast_rows(const float* x, void* out, int out_dtype, long long n, cudaStream_t stream) {
+    if (n <= 0) return 0;
+    const unsigned blocks = (unsigned)((n + 255) / 256 > 8192 ? 8192 : (n + 255) / 256);
+    if (out_dtype == IMPARO_DT_BF16)
+        launch(cast_rows_kernel<__nv_bfloat16>, dim3(blocks), dim3(256), 0, stream, x, (__nv_bfloat16*)out, (size_t)n);
+    else if (out_dtype == IMPARO_DT_F32)
+        launch(cast_rows_kernel<float>, dim3(blocks), dim3(256), 0, stream, x, (float*)out, (size_t)n);
+    else return -1;
+    IMPARO_CHECK_LAUNCH();
+    return 0;
+}
+
+extern "C" int imparo_scale_rows(float* x, long long n, float factor, cudaStream_t stream) {
+    if (n <= 0) return 0;
+    const unsigned blocks = (unsigned)((n + 255) / 256 > 8192 ? 8192 : (n + 255) / 256);
+    launch(scale_rows_kernel, dim3(blocks), dim3(256), 0, stream, x, (size_t)n, factor);
     IMPARO_CHECK_LAUNCH();
     return 0;
 }

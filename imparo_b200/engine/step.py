@@ -35,7 +35,7 @@ class StepBatch:
     """The step's batch on the device.  All index arrays are int32."""
     __slots__ = ("n_tokens", "n_items", "token_ids", "positions", "item_of_token", "item_row_start",
                  "item_slot", "item_start_pos", "tables", "want_rows", "n_want", "max_tokens_per_item",
-                 "max_context", "decode_only", "host", "token_src", "n_single", "fresh_slots")
+                 "max_context", "decode_only", "host", "token_src", "n_single", "fresh_slots", "notes")
 
 
 def _round_up(x: int, m: int) -> int:
@@ -220,6 +220,7 @@ class StepFunction:
         self._ring[self._turn][1] = ev
         d = self._dev
         b = StepBatch()
+        b.notes = {}            # what one part leaves for a later part of the same step (tensors of this step's rows)
         b.n_tokens, b.n_items, b.n_want = T, R, W
         b.token_ids, b.positions, b.item_of_token = (d[offs[i]:offs[i] + T] for i in range(3))
         b.item_row_start = d[offs[3]:offs[3] + R + 1]
@@ -246,6 +247,7 @@ class StepFunction:
     # -- a step whose shape has come before replays its captured graph -----------------------
     def _forward(self, batch: StepBatch) -> Optional[torch.Tensor]:
         cache = self.cache
+        batch.notes = {}         # every pass over the model starts without notes (a dropped recording has left some)
         if batch.fresh_slots is not None and getattr(cache, "n_state_segments", 0):
             # a fresh request's state starts at zero: one kernel over the flat state arena, first in the step's chain
             ops.zero_state_slots(cache.state_arena, cache.state_segments, cache.n_state_segments, batch.fresh_slots,

@@ -114,7 +114,18 @@ def _declare_kernels(lib):
     _declare(lib, "imparo_softcap", [P, c_int64, c_float, S])
     _declare(lib, "imparo_qkv_rotate_store", [P, I, P, P, P, I, I, c_float, P, P, P, P, I, I, I, I, I, I, I, I, c_int64, P, S])
     _declare(lib, "imparo_act_rows_strided", [P, c_int64, P, I, I, I, I, S])
-    _declare(lib, "imparo_attention_any", [P, P, P, I, P, P, P, I, I, I, I, c_float, I, P, I, I, I, I, I, P, S])
+    _declare(lib, "imparo_attention_any", [P, P, P, I, P, P, P, I, I, I, I, c_float, I, c_float, P, I, I, I, I, I, P, S])
+    _declare(lib, "imparo_qkv_prepare_store", [P, c_int64, P, I, P, P, P, I, c_float, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, P, S])
+    _declare(lib, "imparo_out_norm_add", [P, P, P, c_float, P, I, I, I, S])
+    _declare(lib, "imparo_cast_rows", [P, P, I, c_int64, S])
+    _declare(lib, "imparo_scale_rows", [P, c_int64, c_float, S])
+    _declare(lib, "imparo_mamba2_conv", [P, I, c_int64, I, I, I, I, I, P, P, P, P, P, P, P, I, I, I, P, P, P, S])
+    _declare(lib, "imparo_mamba2_scan", [P, P, P, P, P, P, P, I, I, P, I, I, I, I, P, S])
+    _declare(lib, "imparo_mamba2_scan_chunked", [P, P, P, P, P, P, P, I, I, P, I, I, I, I, I, I, P, P, P, P, S])
+    _declare(lib, "imparo_gate_group_rmsnorm", [P, P, I, c_int64, P, c_float, P, I, I, I, I, S])
+    _declare(lib, "imparo_moe_route", [P, I, P, I, I, I, I, I, I, P, P, S])
+    _declare(lib, "imparo_moe_rows", [P, P, P, I, P, P, I, I, I, I, I, I, P, P, S])
+    _declare(lib, "imparo_moe_grouped", [P, P, P, I, P, P, I, I, I, I, I, I, P, P, P, P, S])
     _declare(lib, "imparo_linear_attention_recurrent", [P, P, P, c_int64, I, I, P, P, P, P, I, I, P, I, I, I, P, S])
     _declare(lib, "imparo_linear_attention_chunked", [P, P, P, c_int64, I, I, P, P, P, I, I, P, P, I, I, P, I, I, I, P, S])
 

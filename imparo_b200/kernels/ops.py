@@ -1083,9 +1083,10 @@ def qkv_rotate_store(qkv, positions, item_of_token, inv_freq, n_rot, interleaved
 
 
 def attention_any(q, k_cache, v_cache, positions, item_of_token, table, page_size, n_pages, window, scale, sink,
-                  out, nh, nkv, hd, vd, status) -> None:
+                  out, nh, nkv, hd, vd, status, softcap: float = 0.0) -> None:
     """General attention: any head size hd and value size vd up to 256, optional window, optional sink (one more
-    term of score 0 and no value in the softmax's denominator).  out [T, nh*vd]."""
+    term of score 0 and no value in the softmax's denominator), optional soft cap c > 0 on the scaled scores
+    (c * tanh(score / c)).  out [T, nh*vd]."""
     _cuda(q, k_cache, v_cache, positions, item_of_token, table, out, status)
     T = q.shape[0]
     _need(q.shape == (T, nh * hd) and out.shape == (T, nh * vd) and out.dtype == q.dtype, "attention_any: q/out shapes")
@@ -1095,8 +1096,40 @@ def attention_any(q, k_cache, v_cache, positions, item_of_token, table, page_siz
     _need(table.dtype == torch.int32 and table.dim() == 2, "block table must be int32 [items, blocks]")
     _check(_lib.kernels().imparo_attention_any(
         _ptr(q), _ptr(k_cache), _ptr(v_cache), _code(q), _ptr(positions), _ptr(item_of_token), _ptr(table),
-        table.shape[1], page_size, n_pages, int(window or 0), float(scale), int(bool(sink)), _ptr(out), T, nh, nkv, hd, vd,
-        _ptr(status), _stream()), "attention_any")
+        table.shape[1], page_size, n_pages, int(window or 0), float(scale), int(bool(sink)), float(softcap or 0.0), _ptr(out),
+        T, nh, nkv, hd, vd, _ptr(status), _stream()), "attention_any")
+
+
+def qkv_prepare_store(qkv, bias, positions, item_of_token, inv_freq, n_rot, unit_eps, v_other, v_lambda, v_save, q_out,
+                      k_cache, v_cache, table, page_size, n_pages, nh, nkv, hd, vd, status) -> None:
+    """qkv: float32 [T, nh*hd + nkv*hd + nkv*vd] (a 32-bit product; rows dense, any row stride).  Per head, in 32-bit:
+    + bias (float32 over the same columns, or None), half-split rotation of the first n_rot dimensions of q and k, then
+    q and k divided by sqrt(mean(square) + unit_eps) (unit_eps None: kept as they are); q -> q_out [T, nh*hd], k and v
+    into their pages.  v_other ([T, nkv*vd], the cache's dtype) with v_lambda (a float32 scalar on the device) blends
+    the values: v = (1 - lambda) v + lambda v_other; v_save ([T, nkv*vd]) receives the values before blending."""
+    _need(qkv.is_cuda and qkv.stride(1) == 1 and qkv.dtype == torch.float32, "qkv_prepare_store: a float32 product with dense rows")
+    _cuda(bias, positions, item_of_token, inv_freq, v_other, v_lambda, v_save, q_out, k_cache, v_cache, table, status)
+    T = q_out.shape[0]
+    width = nh * hd + nkv * (hd + vd)
+    _need(tuple(qkv.shape) == (T, width) and q_out.shape[1] == nh * hd, "qkv_prepare_store: widths")
+    _need(bias is None or (bias.dtype == torch.float32 and bias.numel() == width), "qkv_prepare_store: bias float32 over the product's columns")
+    _need(positions.dtype == torch.int32 and item_of_token.dtype == torch.int32 and positions.numel() >= T
+          and item_of_token.numel() >= T, "positions / item_of_token must be int32 per token")
+    _need(k_cache.dtype == q_out.dtype and v_cache.dtype == q_out.dtype, "cache dtype must match activations")
+    _need(k_cache.numel() >= n_pages * page_size * nkv * hd and v_cache.numel() >= n_pages * page_size * nkv * vd,
+          "cache arena smaller than n_pages")
+    _need(table.dtype == torch.int32 and table.dim() == 2, "block table must be int32 [items, blocks]")
+    for t in (v_other, v_save):
+        _need(t is None or (t.dtype == q_out.dtype and t.numel() >= T * nkv * vd), "qkv_prepare_store: v_other / v_save [T, nkv*vd]")
+    _need(v_other is None or (v_lambda is not None and v_lambda.dtype == torch.float32 and v_lambda.numel() >= 1),
+          "qkv_prepare_store: blending needs a float32 scalar on the device")
+    if inv_freq is not None:
+        _need(inv_freq.dtype == torch.float32 and inv_freq.numel() >= n_rot // 2, "inv_freq must be float32 [n_rot/2]")
+    _check(_lib.kernels().imparo_qkv_prepare_store(
+        _ptr(qkv), qkv.stride(0), _ptr(bias), _code(q_out), _ptr(positions), _ptr(item_of_token), _ptr(inv_freq), int(n_rot),
+        -1.0 if unit_eps is None else float(unit_eps), _ptr(v_other), _ptr(v_lambda), _ptr(v_save), _ptr(q_out), _ptr(k_cache),
+        _ptr(v_cache), _ptr(table), table.shape[1], page_size, n_pages, T, nh, nkv, hd, vd, _ptr(status), _stream()),
+        "qkv_prepare_store")
 
 
 # ---- linear attention with decay (csrc/kernels/linear_attention.cu) -------------------------------------------
@@ -1138,3 +1171,152 @@ def linear_attention(qkv: torch.Tensor, q_off: int, k_off: int, v_off: int, deca
         base + q_off * es, base + k_off * es, base + v_off * es, qkv.stride(0), _code(qkv), int(act == "silu"), _ptr(decay),
         _ptr(state), _ptr(item_row_start), _ptr(item_slot), int(n_items), state.shape[0], _ptr(out), heads, dim, vdim,
         _ptr(status), _stream()), "linear_attention")
+
+
+# ---- a norm on a sublayer's output, casts, scaling (csrc/kernels/stream_ops.cu) --------------------------------
+def out_norm_add(x: torch.Tensor, y: torch.Tensor, w: torch.Tensor, eps: float, copy: Optional[torch.Tensor] = None) -> None:
+    """x += y / rms(y) * w row by row (x, y float32 [rows, width]; w float32 [width]).  copy ([rows, width], float32 or
+    bfloat16): also receives the updated rows, for products that read the stream itself."""
+    settle(x)
+    _cuda(x, y, w, copy)
+    n, width = x.shape
+    _need(x.dtype == torch.float32 and y.dtype == torch.float32 and y.shape == x.shape, "out_norm_add: float32 [rows, width]")
+    _need(w.dtype == torch.float32 and w.numel() == width, "out_norm_add: weight float32 [width]")
+    _need(copy is None or copy.shape == x.shape, "out_norm_add: copy must have the stream's shape")
+    _check(_lib.kernels().imparo_out_norm_add(_ptr(x), _ptr(y), _ptr(w), float(eps), _ptr(copy), _code(copy) if copy is not None else F32,
+                                              n, width, _stream()), "out_norm_add")
+
+
+def cast_rows(x: torch.Tensor, out: torch.Tensor) -> None:
+    """out = x in out's dtype (x float32)."""
+    settle(x)
+    _cuda(x, out)
+    _need(x.dtype == torch.float32 and x.numel() == out.numel(), "cast_rows: a float32 source of the same size")
+    _check(_lib.kernels().imparo_cast_rows(_ptr(x), _ptr(out), _code(out), x.numel(), _stream()), "cast_rows")
+
+
+def scale_rows(x: torch.Tensor, factor: float) -> None:
+    """x *= factor in place (float32)."""
+    _cuda(x)
+    _need(x.dtype == torch.float32, "scale_rows: float32")
+    _check(_lib.kernels().imparo_scale_rows(_ptr(x), x.numel(), float(factor), _stream()), "scale_rows")
+
+
+# ---- selective state-space mixer (csrc/kernels/mamba2.cu) --------------------------------------------------------
+def mamba2_conv(proj: torch.Tensor, x_off: int, dt_off: int, channels: int, heads: int, taps: int, w: torch.Tensor,
+                bias: Optional[torch.Tensor], dt_bias: torch.Tensor, state: torch.Tensor, item_row_start, item_of_token,
+                item_slot, n_items: int, xbc: torch.Tensor, dt: torch.Tensor, status: torch.Tensor) -> None:
+    """Causal conv + silu over columns [x_off, x_off + channels) of proj with the slot's conv state (float32
+    [slots, taps-1, channels], moved on afterwards) -> xbc float32 [T, channels]; dt = softplus(proj[:, dt_off + h] +
+    dt_bias[h]) -> float32 [T, heads]."""
+    _need(proj.is_cuda and proj.stride(1) == 1, "mamba2_conv: rows of proj must be dense CUDA memory")
+    _cuda(w, bias, dt_bias, state, item_row_start, item_of_token, item_slot, xbc, dt, status)
+    T = proj.shape[0]
+    _need(x_off + channels <= proj.shape[1] and dt_off + heads <= proj.shape[1], "mamba2_conv: offsets")
+    _need(w.dtype == torch.float32 and tuple(w.shape) == (channels, taps), "mamba2_conv: taps float32 [channels, taps]")
+    _need(bias is None or (bias.dtype == torch.float32 and bias.numel() == channels), "mamba2_conv: bias float32 [channels]")
+    _need(dt_bias.dtype == torch.float32 and dt_bias.numel() == heads, "mamba2_conv: dt_bias float32 [heads]")
+    _need(state.dtype == torch.float32 and tuple(state.shape[1:]) == (max(taps - 1, 1), channels), "mamba2_conv: state float32 [slots, taps-1, channels]")
+    _need(xbc.dtype == torch.float32 and tuple(xbc.shape) == (T, channels) and dt.dtype == torch.float32 and tuple(dt.shape) == (T, heads),
+          "mamba2_conv: outputs float32 [T, channels] and [T, heads]")
+    _need(item_row_start.numel() >= n_items + 1 and item_slot.numel() >= n_items and item_of_token.numel() >= T, "mamba2_conv: item arrays")
+    _check(_lib.kernels().imparo_mamba2_conv(_ptr(proj), _code(proj), proj.stride(0), int(x_off), int(dt_off), int(channels), int(heads),
+                                             int(taps), _ptr(w), _ptr(bias), _ptr(dt_bias), _ptr(state), _ptr(item_row_start),
+                                             _ptr(item_of_token), _ptr(item_slot), int(n_items), state.shape[0], T, _ptr(xbc), _ptr(dt),
+                                             _ptr(status), _stream()), "mamba2_conv")
+    if taps > 1:
+        COUNTS["own"] += 1
+
+
+def mamba2_scan(xbc: torch.Tensor, dt: torch.Tensor, A_log: torch.Tensor, D: torch.Tensor, state: torch.Tensor, item_row_start,
+                item_slot, n_items: int, y: torch.Tensor, heads: int, vdim: int, n_state: int, groups: int, status: torch.Tensor,
+                chunk: int = 0, scratch=None) -> None:
+    """Per request and head, over the request's rows in order, from and into state[slot] (float32 [slots, heads, N, vdim]):
+    S = exp(-exp(A_log) dt) S + dt B x^T;  y = S^T C + D x.  xbc float32 [T, heads*vdim + 2*groups*N] = [x | B | C].
+    chunk > 0 (steps with long portions): the rows of a request are cut into chunks of that many rows that run side by
+    side; scratch = (int32 [3*max_chunks + n_items + 1], float32 [max_chunks*heads*N*vdim], float32 [max_chunks*heads])
+    with max_chunks = T // chunk + n_items.  The result differs from the row-by-row walk by 32-bit rounding only."""
+    _cuda(xbc, dt, A_log, D, state, item_row_start, item_slot, y, status)
+    T = xbc.shape[0]
+    inner = heads * vdim
+    _need(xbc.dtype == torch.float32 and xbc.shape[1] == inner + 2 * groups * n_state, "mamba2_scan: xbc float32 [T, inner + 2 groups N]")
+    _need(dt.dtype == torch.float32 and tuple(dt.shape) == (T, heads), "mamba2_scan: dt float32 [T, heads]")
+    _need(A_log.dtype == torch.float32 and A_log.numel() == heads and D.dtype == torch.float32 and D.numel() == heads,
+          "mamba2_scan: A_log and D float32 [heads]")
+    _need(state.dtype == torch.float32 and tuple(state.shape[1:]) == (heads, n_state, vdim), "mamba2_scan: state float32 [slots, heads, N, vdim]")
+    _need(y.dtype == torch.float32 and tuple(y.shape) == (T, inner), "mamba2_scan: y float32 [T, heads*vdim]")
+    _need(item_row_start.numel() >= n_items + 1 and item_slot.numel() >= n_items, "mamba2_scan: item arrays")
+    if chunk > 0:
+        max_chunks = T // chunk + n_items
+        si, cs, cd = scratch
+        _cuda(si, cs, cd)
+        _need(si.dtype == torch.int32 and si.numel() >= 3 * max_chunks + n_items + 1 and cs.dtype == torch.float32
+              and cs.numel() >= max_chunks * heads * n_state * vdim and cd.dtype == torch.float32 and cd.numel() >= max_chunks * heads,
+              "mamba2_scan: chunk scratch too small")
+        _check(_lib.kernels().imparo_mamba2_scan_chunked(_ptr(xbc), _ptr(dt), _ptr(A_log), _ptr(D), _ptr(state), _ptr(item_row_start),
+                                                         _ptr(item_slot), int(n_items), state.shape[0], _ptr(y), heads, vdim, n_state,
+                                                         groups, int(chunk), int(max_chunks), _ptr(si), _ptr(cs), _ptr(cd), _ptr(status),
+                                                         _stream()), "mamba2_scan_chunked")
+        COUNTS["own"] += 3
+        return
+    _check(_lib.kernels().imparo_mamba2_scan(_ptr(xbc), _ptr(dt), _ptr(A_log), _ptr(D), _ptr(state), _ptr(item_row_start), _ptr(item_slot),
+                                             int(n_items), state.shape[0], _ptr(y), heads, vdim, n_state, groups, _ptr(status),
+                                             _stream()), "mamba2_scan")
+
+
+def gate_group_rmsnorm(y: torch.Tensor, z: torch.Tensor, w: torch.Tensor, eps: float, groups: int, out: torch.Tensor) -> None:
+    """out = (y * silu(z)) normed in `groups` equal stretches of the row (each by its own root mean square), times w.
+    y float32 [rows, width]; z [rows, width], rows may be strided (a stretch of a wider product); out [rows, width]."""
+    _need(y.is_cuda and z.is_cuda and out.is_cuda and w.is_cuda, "kernels run on CUDA tensors only (there is no CPU path)")
+    n, width = out.shape
+    _need(y.dtype == torch.float32 and tuple(y.shape) == (n, width) and y.is_contiguous() and out.is_contiguous(), "gate_group_rmsnorm: y float32 [rows, width]")
+    _need(w.dtype == torch.float32 and w.numel() == width and width % groups == 0, "gate_group_rmsnorm: weight float32 [width], groups divide width")
+    _need(tuple(z.shape) == (n, width) and z.stride(1) == 1, "gate_group_rmsnorm: z [rows, width] with dense rows")
+    _check(_lib.kernels().imparo_gate_group_rmsnorm(_ptr(y), _ptr(z), _code(z), z.stride(0), _ptr(w), float(eps), _ptr(out), _code(out),
+                                                    n, width, int(groups), _stream()), "gate_group_rmsnorm")
+
+
+# ---- routed feed-forward (csrc/kernels/moe.cu) -------------------------------------------------------------------
+def moe_route(h: torch.Tensor, w_router: torch.Tensor, top: int, ids: torch.Tensor, wts: torch.Tensor, softmax: bool = False,
+              renormalise: bool = False) -> None:
+    """Router logits W_r h in 32-bit, sigmoid (or softmax) scores, the `top` largest per row: ids int32 [rows, top],
+    wts float32 [rows, top]."""
+    _cuda(h, w_router, ids, wts)
+    n, width = h.shape
+    E = w_router.shape[0]
+    _need(w_router.dtype == torch.float32 and w_router.shape[1] == width, "moe_route: router float32 [experts, width]")
+    _need(ids.dtype == torch.int32 and wts.dtype == torch.float32 and ids.numel() >= n * top and wts.numel() >= n * top,
+          "moe_route: ids int32 and wts float32 [rows, top]")
+    _check(_lib.kernels().imparo_moe_route(_ptr(h), _code(h), _ptr(w_router), n, width, E, int(top), int(bool(softmax)),
+                                           int(bool(renormalise)), _ptr(ids), _ptr(wts), _stream()), "moe_route")
+
+
+MOE_GROUP_FROM = 32          # steps with at least this many (row, choice) pairs per expert on average run grouped by expert
+
+
+def moe_experts(h: torch.Tensor, w_gu: torch.Tensor, w_down: torch.Tensor, ids: torch.Tensor, wts: torch.Tensor, top: int,
+                weight_input: bool, mid: torch.Tensor, out: torch.Tensor, scratch=None) -> None:
+    """out[r] = sum_k expert_{ids[r,k]}(wts[r,k] * h[r])  (weight_input) or sum_k wts[r,k] * expert(h[r]).
+    w_gu [experts, 2 ff, width] = [gate; up], w_down [experts, width, ff]; mid [rows*top, ff] in h's dtype; out float32
+    [rows, width], overwritten.  scratch = (float32 [rows*top, width], int32 [rows*top + experts + 2 + 3*(rows*top//32 + experts)]):
+    when given, pairs are sorted by expert and run as tiles (steps of many rows); else each pair on its own."""
+    _cuda(h, w_gu, w_down, ids, wts, mid, out)
+    n, width = h.shape
+    E, ff2, _ = w_gu.shape
+    ff = ff2 // 2
+    _need(w_gu.dtype == h.dtype and w_down.dtype == h.dtype and mid.dtype == h.dtype, "moe_experts: one dtype for h, the experts and mid")
+    _need(w_gu.shape[2] == width and tuple(w_down.shape) == (E, width, ff), "moe_experts: expert shapes")
+    _need(mid.numel() >= n * top * ff and out.dtype == torch.float32 and tuple(out.shape) == (n, width), "moe_experts: mid / out sizes")
+    if scratch is not None:
+        pair_out, si = scratch
+        _cuda(pair_out, si)
+        _need(pair_out.dtype == torch.float32 and pair_out.numel() >= n * top * width and si.dtype == torch.int32
+              and si.numel() >= n * top + E + 2 + 3 * (n * top // 32 + E), "moe_experts: grouped scratch too small")
+        _check(_lib.kernels().imparo_moe_grouped(_ptr(h), _ptr(w_gu), _ptr(w_down), _code(h), _ptr(ids), _ptr(wts), n, width, ff, int(top),
+                                                 E, int(bool(weight_input)), _ptr(mid), _ptr(pair_out), _ptr(si), _ptr(out), _stream()),
+               "moe_grouped")
+        COUNTS["own"] += 3
+        return
+    _check(_lib.kernels().imparo_moe_rows(_ptr(h), _ptr(w_gu), _ptr(w_down), _code(h), _ptr(ids), _ptr(wts), n, width, ff, int(top), E,
+                                          int(bool(weight_input)), _ptr(mid), _ptr(out), _stream()), "moe_rows")
+    COUNTS["own"] += 1

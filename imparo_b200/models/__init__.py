@@ -1,3 +1,4 @@
 """Built-in architectures; importing this package registers them."""
 from . import lfm2  # noqa: F401
 from . import vipotar  # noqa: F401
+from . import negotar  # noqa: F401

@@ -23,7 +23,12 @@ class AttentionMixer(Part):
     no norm tensors are declared), bias (bool, default False: True declares optional q/k/v/out biases, used
     when the file carries them), names (optional dict of tensor names), v_head_dim (the value size per head, default
     head_dim), scale (the factor on q.k, default 1/sqrt(head_dim)), sink (bool, default False: the softmax's denominator
-    counts one more term of score 0 that has no value, p_j = exp(s_j) / (1 + sum exp(s_j))).
+    counts one more term of score 0 that has no value, p_j = exp(s_j) / (1 + sum exp(s_j))), softcap (c > 0: the scaled
+    score becomes c * tanh(score / c)), unit_norm (bool: after the rotation q and k are divided by their own root mean
+    square per head, eps as given, no weight), bias "required" (q/k/v biases that the file must carry, added in 32-bit
+    before the rotation), v_share ({"role": "source" | "blend", "lambda": tensor name}: the source layer leaves the values
+    it made for the step's rows to later layers of the same step; a blending layer stores (1 - lambda) v + lambda v_source,
+    lambda its own scalar tensor).
 
     Shapes and variants the specialised kernels do not take (a value size of its own, a sink, a rotation of interleaved
     pairs or with a magnitude, a head size that is no multiple of 16) run on the general pair of kernels
@@ -61,11 +66,23 @@ class AttentionMixer(Part):
         self.position = make_part("position", p.get("position", PartSpec("none")), prefix, rt)
         # the general kernels take what the specialised ones (per-head norm + half-split rotation, equal sizes,
         # plain softmax) do not
+        self.softcap = float(p["softcap"]) if p.get("softcap") else 0.0
+        self.unit_norm = bool(p.get("unit_norm", False))
+        self.v_share = dict(p["v_share"]) if p.get("v_share") else None
+        if self.v_share is not None and self.v_share.get("role") not in ("source", "blend"):
+            raise ValueError("attention: v_share role must be 'source' or 'blend'")
+        self.bias_required = p.get("bias") == "required"
+        # whole heads in 32-bit before anything is rounded: biases, rotation, the norm without a weight, shared values
+        self.prepared = self.unit_norm or self.v_share is not None or self.bias_required
         self.general = (self.sink or self.vd != self.hd or self.hd % 16 != 0 or self.position.interleaved
-                        or self.position.magnitude != 1.0)
-        if self.general and (self.qk_norm or self.bias):
+                        or self.position.magnitude != 1.0 or self.prepared or self.softcap > 0.0)
+        if self.prepared and (self.qk_norm or self.position.interleaved or self.position.magnitude != 1.0):
+            raise ValueError("attention: the 32-bit head preparation (unit_norm, v_share, required biases) takes a half-split "
+                             "rotation and no weighted q/k norms")
+        if self.general and not self.prepared and (self.qk_norm or self.bias):
             raise ValueError("attention: per-head q/k norms and biases are not available together with a sink, a value size "
                              "of its own, an interleaved or scaled rotation, or a head size that is no multiple of 16")
+        self.v_lambda = None
         self.w_qkv = self.w_o = self.q_norm = self.k_norm = self.b_qkv = self.b_o = None
 
     def weight_specs(self):
@@ -75,11 +92,17 @@ class AttentionMixer(Part):
         if self.qk_norm:
             specs += [WeightSpec(n["q_norm"], ((hd,),), role="vector", init=("norm",)),
                       WeightSpec(n["k_norm"], ((hd,),), role="vector", init=("norm",))]
-        if self.bias:
+        if self.bias_required:
+            specs += [WeightSpec(n["q_bias"], ((self.nh * hd,),), role="vector", init=("bias",)),
+                      WeightSpec(n["k_bias"], ((self.nkv * hd,),), role="vector", init=("bias",)),
+                      WeightSpec(n["v_bias"], ((self.nkv * vd,),), role="vector", init=("bias",))]
+        elif self.bias:
             specs += [WeightSpec(n["q_bias"], ((self.nh * hd,),), role="vector", init=("bias",), optional=True),
                       WeightSpec(n["k_bias"], ((self.nkv * hd,),), role="vector", init=("bias",), optional=True),
                       WeightSpec(n["v_bias"], ((self.nkv * hd,),), role="vector", init=("bias",), optional=True),
                       WeightSpec(n["o_bias"], ((H,),), role="vector", init=("bias",), optional=True)]
+        if self.v_share is not None:
+            specs.append(WeightSpec(self.prefix + self.v_share["lambda"], ((),), role="vector", init=("uniform", 0.2, 0.8)))
         return specs + self.position.weight_specs()
 
     def bind(self, tensors):
@@ -89,9 +112,11 @@ class AttentionMixer(Part):
         self.w_o = tensors[n["o"]]
         self.q_norm = tensors[n["q_norm"]] if self.qk_norm else None
         self.k_norm = tensors[n["k_norm"]] if self.qk_norm else None
+        if self.v_share is not None:
+            self.v_lambda = tensors[self.prefix + self.v_share["lambda"]].reshape(1).float().contiguous()
         if self.bias:
             parts = [(tensors.get(n["q_bias"]), self.nh * self.hd), (tensors.get(n["k_bias"]), self.nkv * self.hd),
-                     (tensors.get(n["v_bias"]), self.nkv * self.hd)]
+                     (tensors.get(n["v_bias"]), self.nkv * self.vd)]
             if any(t is not None for t, _ in parts):      # one vector [q | k | v], zeros where the file has none
                 ref = self.w_o
                 self.b_qkv = torch.cat([t.float() if t is not None else torch.zeros(w, dtype=torch.float32, device=ref.device)
@@ -115,7 +140,7 @@ class AttentionMixer(Part):
         return (8 * ops.sm_count() + rows * self.nkv * (1 + -(-context // 512))) * (self.nh // self.nkv)
 
     def input_rows(self) -> int:
-        return self.nh * self.hd + self.nkv * (self.hd + self.vd) if self.general else 0
+        return self.nh * self.hd + self.nkv * (self.hd + self.vd) if self.general and not self.prepared else 0
 
     def input_weight(self):
         return self.w_qkv
@@ -129,20 +154,40 @@ class AttentionMixer(Part):
         nh, hd, vd = self.nh, self.hd, self.vd
         nkv = self.nkv if kv.writes else 0
         width = nh * hd + nkv * (hd + vd)
-        if projected is not None and kv.writes:
-            qkv = projected
-        else:
-            qkv = rt.workspace.get("attn_qkv", (T, width), rt.act_dtype, first="tokens")
-            ops.linear(x, self.w_qkv[:width], qkv, status=rt.status)
         q = rt.workspace.get("attn_q", (T, nh * hd), rt.act_dtype, first="tokens")
         rot = self.position.rotary()
         inv_freq, n_rot = rot if rot is not None else (None, 0)
         table = batch.tables[kv.group]
-        ops.qkv_rotate_store(qkv, batch.positions, batch.item_of_token, inv_freq, n_rot, self.position.interleaved,
-                             self.position.magnitude, q, kv.k, kv.v, table, kv.page_size, kv.n_pages, nh, nkv, hd, vd, rt.status)
+        if self.prepared:
+            if not kv.writes:
+                raise ValueError("attention: a layer that reads another entry's cache cannot prepare heads in 32-bit")
+            # the product in 32-bit, so that biases, angles and the norm without a weight see unrounded heads
+            qkv = rt.workspace.get("attn_qkv32", (T, width), torch.float32, first="tokens")
+            ops.linear(x, self.w_qkv[:width], qkv, status=rt.status)
+            v_other = v_save = None
+            if self.v_share is not None:
+                notes = batch.notes
+                key = ("v_share", nkv * vd)
+                if self.v_share["role"] == "source":
+                    v_save = notes[key] = rt.workspace.get("attn_v_shared", (T, nkv * vd), rt.act_dtype, first="tokens")
+                else:
+                    v_other = notes.get(key)
+                    if v_other is None:
+                        raise ValueError("attention: a layer blends shared values, but no earlier layer of the step left any")
+            ops.qkv_prepare_store(qkv, self.b_qkv, batch.positions, batch.item_of_token, inv_freq, n_rot,
+                                  self.eps if self.unit_norm else None, v_other, self.v_lambda if v_other is not None else None,
+                                  v_save, q, kv.k, kv.v, table, kv.page_size, kv.n_pages, nh, nkv, hd, vd, rt.status)
+        else:
+            if projected is not None and kv.writes:
+                qkv = projected
+            else:
+                qkv = rt.workspace.get("attn_qkv", (T, width), rt.act_dtype, first="tokens")
+                ops.linear(x, self.w_qkv[:width], qkv, status=rt.status)
+            ops.qkv_rotate_store(qkv, batch.positions, batch.item_of_token, inv_freq, n_rot, self.position.interleaved,
+                                 self.position.magnitude, q, kv.k, kv.v, table, kv.page_size, kv.n_pages, nh, nkv, hd, vd, rt.status)
         out = rt.workspace.get("attn_out", (T, nh * vd), rt.act_dtype, first="tokens")
         done = False
-        if rt.act_dtype == torch.bfloat16 and hd == vd and hd in (64, 128) and nh // self.nkv <= 8 and T <= 65535:
+        if self.softcap == 0.0 and rt.act_dtype == torch.bfloat16 and hd == vd and hd in (64, 128) and nh // self.nkv <= 8 and T <= 65535:
             # the tensor-core kernels take these sizes (the sink as a flag): prompt portions on the tcgen05 kernel, rows
             # of one token (and portions too short for a tile, or pages it does not take) on the split-key kernel
             n1 = getattr(batch, "n_single", 0)
@@ -170,7 +215,7 @@ class AttentionMixer(Part):
                                                  chunk, n_splits, nh, self.nkv, hd, rt.status, sink=self.sink)
         if not done:
             ops.attention_any(q, kv.k, kv.v, batch.positions, batch.item_of_token, table, kv.page_size, kv.n_pages, self.window,
-                              self.scale, self.sink, out, nh, self.nkv, hd, vd, rt.status)
+                              self.scale, self.sink, out, nh, self.nkv, hd, vd, rt.status, softcap=self.softcap)
         ops.linear(out, self.w_o, residual, accumulate=accumulate, status=rt.status)
 
     def forward(self, x, batch, caches, residual, accumulate=True, projected=None):

@@ -197,3 +197,96 @@ class ParallelResidualBlock(Block):
         if probe:
             probe("stream_out", x)
         return None
+
+
+class OutputNormResidualBlock(Block):
+    """The norm sits on each sublayer's OUTPUT only:  x += norm1(mixer(x));  x += norm2(feed_forward(x)).
+
+    params: layer (LayerSpec): mixer_norm is norm1, feed_forward_norm norm2 (both "rmsnorm" parts; their weight and eps
+    are what the add kernel applies); feed_forward may be None.  The sublayers read the stream itself: in 32-bit the
+    stream, in bfloat16 its rounding, which the add kernel of the sublayer before stores beside the updated stream
+    (batch.notes["stream_copy"]; the first block of a step makes it with a cast).  Sublayers write their output into a
+    float32 buffer (forward(..., accumulate=False)); one kernel norms it and adds it into the stream."""
+
+    def __init__(self, params, prefix, rt):
+        super().__init__(params, prefix, rt)
+        spec = params["layer"]
+        self.mixer_norm = make_part("norm", spec.mixer_norm, prefix, rt)
+        self.mixer = make_part("mixer", spec.mixer, prefix, rt)
+        self.ff = make_part("feed_forward", spec.feed_forward, prefix, rt) if spec.feed_forward is not None else None
+        self.ff_norm = make_part("norm", spec.feed_forward_norm, prefix, rt) if self.ff is not None else None
+        self.parts = tuple(p for p in (self.mixer_norm, self.mixer, self.ff_norm, self.ff) if p is not None)
+        self.graph_safe = all(p.graph_safe for p in self.parts)
+        self.picks_rows = True
+
+    def weight_specs(self):
+        return [w for p in self.parts for w in p.weight_specs()]
+
+    def bind(self, tensors):
+        for p in self.parts:
+            p.bind(tensors)
+
+    def cache_specs(self):
+        return self.mixer.cache_specs()
+
+    def _input(self, x, batch, tag="stream_copy"):
+        """What the sublayer's products read: the stream (32-bit path) or its copy in the activation dtype."""
+        import torch
+        from ..kernels import ops
+        if self.rt.act_dtype == torch.float32:
+            return x
+        notes = getattr(batch, "notes", None)
+        if notes is not None and notes.get("stream_copy_of") == x.data_ptr():
+            return notes["stream_copy"]
+        h = self.rt.workspace.get(tag, tuple(x.shape), self.rt.act_dtype, first="tokens" if tag == "stream_copy" else "rows")
+        ops.cast_rows(x, h)
+        return h
+
+    def _add(self, x, y, norm, batch, tag="stream_copy"):
+        """x += norm(y); in bfloat16 the updated rows are also left as the next sublayer's input."""
+        import torch
+        from ..kernels import ops
+        copy = None
+        if self.rt.act_dtype != torch.float32:
+            copy = self.rt.workspace.get(tag, tuple(x.shape), self.rt.act_dtype, first="tokens" if tag == "stream_copy" else "rows")
+        ops.out_norm_add(x, y, norm.weight, norm.eps, copy=copy)
+        notes = getattr(batch, "notes", None)
+        if copy is not None and notes is not None and tag == "stream_copy":
+            notes["stream_copy"], notes["stream_copy_of"] = copy, x.data_ptr()
+        return copy if copy is not None else x
+
+    def forward(self, x, batch, caches, only_rows=None):
+        import torch
+        from ..kernels import ops
+        probe = self.rt.probe if self.rt.probe_now else None
+        ws = self.rt.workspace
+        ops.settle(x)
+        if probe:
+            probe("stream_in", x)
+        y = ws.get("sublayer_out", tuple(x.shape), torch.float32, first="tokens")
+        self.mixer.forward(self._input(x, batch), batch, caches, y, accumulate=False)
+        ops.settle(y)
+        h = self._add(x, y, self.mixer_norm, batch)
+        if probe:
+            probe("stream_mixer", x)
+        if only_rows is not None:
+            rows, n = only_rows
+            if n == 0:
+                return None
+            xs = ws.get("stream_picked", (n, x.shape[1]), x.dtype, first="rows")
+            ops.gather_rows(x, rows, xs)
+            if self.ff is not None:
+                ys = ws.get("sublayer_out_picked", (n, x.shape[1]), torch.float32, first="rows")
+                self.ff.forward(self._input(xs, None, tag="stream_copy_picked"), batch, ys, accumulate=False)
+                ops.settle(ys)
+                self._add(xs, ys, self.ff_norm, None, tag="stream_copy_picked")
+            if probe:
+                probe("stream_out", xs)
+            return xs
+        if self.ff is not None:
+            self.ff.forward(h, batch, y, accumulate=False)
+            ops.settle(y)
+            self._add(x, y, self.ff_norm, batch)
+        if probe:
+            probe("stream_out", x)
+        return None

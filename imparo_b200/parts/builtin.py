@@ -1,10 +1,12 @@
 """Registers the built-in parts."""
 from .attention import AttentionMixer
 from .base import register_part
-from .block import ParallelResidualBlock, PreNormResidualBlock
+from .block import OutputNormResidualBlock, ParallelResidualBlock, PreNormResidualBlock
 from .embedding import LinearHead, TokenEmbedding
 from .feedforward import DenseFeedForward, SwiGLU
 from .linear_attention import DecayLinearAttention
+from .mamba2 import Mamba2Mixer
+from .moe import RoutedExperts
 from .norm import RMSNorm
 from .position import NoPosition, RotaryInterleaved, RotaryNeox
 from .shortconv import ShortConvMixer
@@ -26,3 +28,6 @@ register_part("feed_forward", "dense", DenseFeedForward, replace=True)
 register_part("position", "rope_interleaved", RotaryInterleaved, replace=True)
 register_part("block", "parallel_residual", ParallelResidualBlock, replace=True)
 register_part("stream_op", "stretch_entry", StretchEntry, replace=True)
+register_part("block", "outnorm_residual", OutputNormResidualBlock, replace=True)
+register_part("mixer", "mamba2", Mamba2Mixer, replace=True)
+register_part("feed_forward", "routed_experts", RoutedExperts, replace=True)

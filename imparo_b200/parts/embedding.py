@@ -38,8 +38,8 @@ class TokenEmbedding(Part):
 
 
 class LinearHead(Part):
-    """params: vocab, width, name (the table's own tensor, or the embedding's when tied), softcap (optional c > 0:
-    logits become c * tanh(logits / c))."""
+    """params: vocab, width, name (the table's own tensor, or the embedding's when tied), scale (optional factor on
+    the logits, applied in 32-bit before any cap), softcap (optional c > 0: logits become c * tanh(logits / c))."""
 
     def __init__(self, params, prefix, rt):
         super().__init__(params, prefix, rt)
@@ -47,6 +47,7 @@ class LinearHead(Part):
         self.width = int(params["width"])
         self.name = prefix + params["name"]
         self.softcap = float(params["softcap"]) if params.get("softcap") else None
+        self.scale = float(params["scale"]) if params.get("scale") is not None else 1.0
         self.table = None
 
     def weight_specs(self):
@@ -58,6 +59,8 @@ class LinearHead(Part):
     def forward(self, h: torch.Tensor) -> torch.Tensor:
         logits = self.rt.workspace.get("logits", (h.shape[0], self.vocab), torch.float32, first="rows")
         ops.linear(h, self.table, logits, status=self.rt.status)
+        if self.scale != 1.0:
+            ops.scale_rows(logits, self.scale)
         if self.softcap is not None:
             ops.softcap(logits, self.softcap)
         return logits

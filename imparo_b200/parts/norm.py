@@ -1,5 +1,6 @@
 """RMS norm as a part: y = x * 1/sqrt(mean(x^2) + eps) * w, sums in 32-bit
-(imparo-cpu/src/ops.rs:6-22)."""
+(imparo-cpu/src/ops.rs:6-22).  With `offset` the stored tensor is the weight's distance from that number
+(offset 1: the file keeps w - 1, y = x / rms * (1 + stored))."""
 from __future__ import annotations
 
 from typing import Optional
@@ -12,20 +13,25 @@ from .spec import WeightSpec
 
 
 class RMSNorm(Part):
-    """params: width, eps, name (tensor name after the prefix, e.g. "operator_norm.weight")."""
+    """params: width, eps, name (tensor name after the prefix, e.g. "operator_norm.weight"), offset (default 0: the
+    stored tensor is the weight; c: the weight is c + the stored tensor, added once in 32-bit when the tensor is bound)."""
 
     def __init__(self, params, prefix, rt):
         super().__init__(params, prefix, rt)
         self.width = int(params["width"])
         self.eps = float(params["eps"])
         self.name = prefix + params["name"]
+        self.offset = float(params.get("offset", 0.0))
         self.weight: Optional[torch.Tensor] = None
 
     def weight_specs(self):
-        return [WeightSpec(self.name, ((self.width,),), role="vector", init=("norm",))]
+        init = ("norm",) if self.offset == 0.0 else ("norm_offset", self.offset)
+        return [WeightSpec(self.name, ((self.width,),), role="vector", init=init)]
 
     def bind(self, tensors):
         self.weight = tensors[self.name]
+        if self.offset != 0.0:
+            self.weight = (self.weight.float() + self.offset).contiguous()
 
     def forward(self, x: torch.Tensor, rows: Optional[torch.Tensor] = None, n_rows: Optional[int] = None,
                 tag: str = "normed") -> torch.Tensor:

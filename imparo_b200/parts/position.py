@@ -33,7 +33,11 @@ class NoPosition(PositionEncoding):
 
 
 class RotaryNeox(PositionEncoding):
-    """params: head_dim, theta, n_rot (default head_dim)."""
+    """params: head_dim, theta, n_rot (default head_dim), wavelength_scaling (optional: factor, low, high, original).
+
+    With wavelength_scaling a pair's frequency f depends on its wavelength l = 2 pi / f: kept where l < original / high,
+    f / factor where l > original / low, and between the two (1 - s) f / factor + s f with
+    s = (original / l - low) / (high - low).  Computed in 64-bit on the host, kept as a 32-bit table."""
 
     def __init__(self, params, prefix, rt):
         super().__init__(params, prefix, rt)
@@ -43,11 +47,19 @@ class RotaryNeox(PositionEncoding):
         if self.n_rot % 2 or self.n_rot > self.head_dim:
             raise ValueError(f"rotary: n_rot {self.n_rot} must be even and at most the head size {self.head_dim}")
         i = torch.arange(self.n_rot // 2, dtype=torch.float64)
-        inv = torch.pow(torch.tensor(self.theta, dtype=torch.float64), -2.0 * i / self.n_rot).to(torch.float32)
-        self.inv_freq = inv.to(rt.device)
+        inv = torch.pow(torch.tensor(self.theta, dtype=torch.float64), -2.0 * i / max(self.n_rot, 1))
+        sc = params.get("wavelength_scaling")
+        if sc:
+            import math
+            factor, low, high, original = (float(sc[k]) for k in ("factor", "low", "high", "original"))
+            wavelength = 2.0 * math.pi / inv
+            s = (original / wavelength - low) / (high - low)
+            blended = (1.0 - s) * inv / factor + s * inv
+            inv = torch.where(wavelength < original / high, inv, torch.where(wavelength > original / low, inv / factor, blended))
+        self.inv_freq = inv.to(torch.float32).to(rt.device)
 
     def rotary(self):
-        return self.inv_freq, self.n_rot
+        return (self.inv_freq, self.n_rot) if self.n_rot else None
 
 
 class RotaryInterleaved(PositionEncoding):

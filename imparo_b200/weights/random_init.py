@@ -4,7 +4,8 @@ configuration and a seed.
 The reference has no such mode (its tests build plans in code and never weights,
 imparo-model/src/lfm2/workflow_gpu.rs:2204-2261).  Distributions: matrices and the
 embedding N(0, matrix_std); conv taps N(0, conv_std); biases N(0, matrix_std); norm weights
-1 + U(-norm_jitter, norm_jitter) (norm_jitter 0 gives exactly 1).  One generator, seeded
+1 + U(-norm_jitter, norm_jitter) (norm_jitter 0 gives exactly 1; drawn as U(-norm_jitter, norm_jitter) for norms that add an
+offset); ("uniform", low, high) for constants with a range of their own.  One generator, seeded
 once, drawn from in the order the model declares its tensors, always in float32 and
 rounded to the stored dtype afterwards.
 """
@@ -48,6 +49,10 @@ def draw_random_tensors(specs, seed: int, dtype: str = "bfloat16", device="cpu",
             t = torch.randn(shape, generator=gen, dtype=torch.float32, device=device) * float(matrix_std)
         elif kind == "normal":
             t = torch.randn(shape, generator=gen, dtype=torch.float32, device=device) * float(w.init[1] if len(w.init) > 1 else matrix_std)
+        elif kind == "norm_offset":          # a norm weight stored as its distance from w.init[1]
+            t = (torch.rand(shape, generator=gen, dtype=torch.float32, device=device) * 2.0 - 1.0) * float(norm_jitter)
+        elif kind == "uniform":              # ("uniform", low, high)
+            t = float(w.init[1]) + torch.rand(shape, generator=gen, dtype=torch.float32, device=device) * (float(w.init[2]) - float(w.init[1]))
         elif kind == "ones":
             t = torch.ones(shape, dtype=torch.float32, device=device)
         elif kind == "zeros":
