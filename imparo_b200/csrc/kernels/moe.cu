@@ -40,18 +40,15 @@ moe_route_kernel(const T* __restrict__ h, const float* __restrict__ w_r, int n_r
         if (lane == 0) s[e] = acc;
     }
     __syncwarp();
+    // The choice goes by the logits: scores are monotone in them, and a sigmoid that has reached 1 in 32-bit would tie.
+    float m = -INFINITY, l = 1.f;
     if (softmax_scores) {
-        float m = -INFINITY;
         for (int e = lane; e < experts; e += 32) m = fmaxf(m, s[e]);
         m = warp_max(m);
-        float l = 0.f;
+        l = 0.f;
         for (int e = lane; e < experts; e += 32) l += expf(s[e] - m);
         l = warp_sum(l);
-        for (int e = lane; e < experts; e += 32) s[e] = expf(s[e] - m) / l;
-    } else {
-        for (int e = lane; e < experts; e += 32) s[e] = 1.0f / (1.0f + expf(-s[e]));
     }
-    __syncwarp();
     float total = 0.f;
     for (int k = 0; k < top; ++k) {
         float best = -INFINITY;
@@ -66,12 +63,13 @@ moe_route_kernel(const T* __restrict__ h, const float* __restrict__ w_r, int n_r
             const int oa = __shfl_xor_sync(0xffffffffu, arg, o);
             if (ob > best || (ob == best && oa < arg)) { best = ob; arg = oa; }
         }
+        const float score = softmax_scores ? expf(best - m) / l : 1.0f / (1.0f + expf(-best));
         if (lane == 0) {
             ids[(size_t)r * top + k] = arg;
-            wts[(size_t)r * top + k] = best;
+            wts[(size_t)r * top + k] = score;
             s[arg] = -INFINITY;
         }
-        total += best;
+        total += score;
         __syncwarp();
     }
     if (renormalise && lane < top) wts[(size_t)r * top + lane] /= total;

@@ -192,10 +192,17 @@ def mamba2_mixer(h, W, prefix, m, eps):
 # feed-forward
 # ----------------------------------------------------------------------------
 
-def routed_experts(h, W, prefix, mlp):
-    """Sigmoid router, the `top` best experts, the score multiplies the expert's INPUT; no renormalisation."""
+def routed_experts(h, W, prefix, mlp, gaps=None):
+    """Sigmoid router, the `top` best experts, the score multiplies the expert's INPUT; no renormalisation.
+    gaps: a list that receives, per row, how far the last chosen expert's router logit lies above the first one left
+    out, as a fraction of the logits' root mean square (inf when every expert is used): small means a close call."""
     E, top = int(mlp["router"]["experts"]), int(mlp["router"]["top"])
-    s = sigmoid(h @ W[prefix + "router"].T)
+    z = h @ W[prefix + "router"].T
+    s = sigmoid(z)
+    if gaps is not None:
+        zs = -np.sort(-z, axis=1)
+        spread = np.maximum(np.sqrt(np.mean(z * z, axis=1)), 1e-3)
+        gaps.append((zs[:, top - 1] - zs[:, top]) / spread if top < E else np.full(len(z), np.inf))
     out = np.zeros_like(h)
     for t in range(h.shape[0]):
         chosen = sorted(range(E), key=lambda e: (-s[t, e], e))[:top]
@@ -210,9 +217,9 @@ def routed_experts(h, W, prefix, mlp):
 # the model
 # ----------------------------------------------------------------------------
 
-def forward(cfg, W, tokens, dtype=np.float64, streams=None):
+def forward(cfg, W, tokens, dtype=np.float64, streams=None, gaps=None):
     """Logits [T, vocab] of one sequence.  W: tensor name -> numpy array.  streams: a list that receives the
-    residual stream after every layer."""
+    residual stream after every layer; gaps: a list that receives every routed layer's per-row gaps (routed_experts)."""
     W = {k: np.asarray(v).astype(dtype) for k, v in W.items()}
     eps = float(cfg["norm"]["eps"])
     x = W["embed"][np.asarray(tokens)]
@@ -233,7 +240,7 @@ def forward(cfg, W, tokens, dtype=np.float64, streams=None):
             raise ValueError(f"unknown layer type {L['type']}")
         x = x + offset_norm(y, W[p + "norm1"], eps)
         if L.get("mlp") is not None:
-            x = x + offset_norm(routed_experts(x, W, p + "mlp.", L["mlp"]), W[p + "norm2"], eps)
+            x = x + offset_norm(routed_experts(x, W, p + "mlp.", L["mlp"], gaps), W[p + "norm2"], eps)
         if streams is not None:
             streams.append(x.copy())
     h = offset_norm(x, W["final.norm"], eps)

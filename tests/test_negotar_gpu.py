@@ -1,0 +1,570 @@
+"""Negotar on the GPU against the plain implementation (tests/plain/negotar_plain.py), in 32-bit and bfloat16:
+each mechanism's kernel alone, the replay families (whole, last tokens one by one, portions down to two tokens,
+mixed batches with pages and slots used again), a far key made to stand out among hundreds and at page borders, a far
+token carried by the recurrent state, the first tokens of a sequence, long decoding, long portions (the chunked
+recurrence, the experts in tiles), and greedy generation through Engine.generate, the command line and bin/trace_run."""
+import functools
+import json
+import os
+import subprocess
+import sys
+import tempfile
+
+import numpy as np
+import pytest
+
+from tests import traces
+from tests.negotar_configs import ALL, PAGE
+from tests.plain import negotar_plain as P
+from tests.plain.lfm2_plain import read_safetensors
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+# Fractions of the largest |logit| of the compared requests.  float32 is the sharp test.  bfloat16: the design norms every
+# sublayer's output (scale-free), so the rounding of a small output is amplified; three positions in four stay within TOL
+# and none leaves WORST (a wrong key, state or expert moves a position by the scale itself).
+#
+# A router's choice between two experts whose logits nearly tie is decided by rounding, and the other expert's output is
+# another vector altogether.  In bfloat16 the places where the plain implementation sees such a tie (the gap between the
+# last expert taken and the first one left out below CLOSE of the logits' spread), and the place after each, are
+# held to no bound; they must stay a minority.  32-bit keeps every place.
+TOL = {"float32": 3e-5, "bfloat16": 3e-2}
+WORST = {"float32": 3e-5, "bfloat16": 0.5}
+CLOSE = 0.03
+_tmp = tempfile.TemporaryDirectory(prefix="imparo_b200_negotar_")
+
+
+def all_errors(steps, got, want):
+    at, out = {}, []
+    for s in steps:
+        r = 0
+        for e in s["entries"]:
+            start = at.get(e["id"], 0)
+            for w in e["want"]:
+                out.append((s["step"], e["id"], start + w, float(np.abs(got[s["step"]][r] - want[s["step"]][r]).max())))
+                r += 1
+            at[e["id"]] = start + len(e["tokens"])
+        for name in s["end"]:
+            at.pop(name, None)
+    return out
+
+
+def rescale(path, change=None):
+    """The drawn matrices are small beside the biases, and then every token looks alike to the layers.  Matrices are
+    scaled to a standard deviation of 1 / sqrt(columns) (the embedding to 1), so that tokens, projections, biases, gates
+    and routers all weigh in.  change: name -> array, tensors to replace."""
+    import torch
+    from imparo_b200.weights.safetensors_io import write_safetensors
+    out = {}
+    for k, v in read_safetensors(path).items():
+        t = torch.as_tensor(np.asarray((change or {}).get(k, v)))
+        if v.ndim == 2 and not k.endswith(".conv"):
+            t = t / t.std() * (1.0 if k == "embed" else 1.0 / np.sqrt(v.shape[1]))
+            t = t.to(torch.float32 if k.endswith(".router") else torch.bfloat16)
+        out[k] = t
+    write_safetensors(path, out)
+
+
+@functools.lru_cache(maxsize=None)
+def model_dir(name, seed=1):
+    from imparo_b200.weights import write_random_model
+    d = os.path.join(_tmp.name, f"{name}_{seed}")
+    write_random_model(d, ALL[name], seed=seed, dtype="bfloat16", norm_jitter=0.3)
+    rescale(os.path.join(d, "model.safetensors"))
+    return d
+
+
+@functools.lru_cache(maxsize=None)
+def weights(name, seed=1):
+    return read_safetensors(os.path.join(model_dir(name, seed), "model.safetensors"))
+
+
+def make_requests(name, lengths, seed=0):
+    rng = np.random.default_rng(seed)
+    return {f"r{i}": rng.integers(0, ALL[name]["vocab"], n).tolist() for i, n in enumerate(lengths)}
+
+
+_plain, _ties = {}, {}
+
+
+def plain_logits(name, requests, seed=1):
+    out = {}
+    for rid, toks in requests.items():
+        key = (name, seed, tuple(toks))
+        if key not in _plain:
+            gaps = []
+            _plain[key] = P.forward(ALL[name], weights(name, seed), toks, gaps=gaps)
+            tie = np.min(np.stack(gaps), axis=0) < CLOSE if gaps else np.zeros(len(toks), dtype=bool)
+            near = tie.copy()
+            for back in (1,):
+                near[back:] |= tie[:-back]
+            _ties[key] = near
+        out[rid] = _plain[key]
+    return out
+
+
+def tied(name, requests, seed=1):
+    """request -> per position: a router of the plain implementation saw a near tie there or just before."""
+    plain_logits(name, requests, seed)
+    return {rid: _ties[(name, seed, tuple(toks))] for rid, toks in requests.items()}
+
+
+def engine_for(name, dtype, steps, parallel=4, page=None, **kw):
+    from imparo_b200.engine import Engine
+    page = page or PAGE[name]
+    max_tokens = traces.max_live_tokens(steps, max(64, page))
+    return Engine(model_dir(name), dtype=dtype, ctx=max_tokens, parallel=parallel, page_size=page,
+                  num_pages=(max_tokens + page - 1) // page, max_step_tokens=max(256, max_tokens), **kw)
+
+
+def check_trace(engine, steps, name, requests, dtype, share=0.25):
+    from tests.gpu_helpers import run_trace
+    ref = plain_logits(name, requests)
+    want = traces.expected(steps, ref)
+    got = run_trace(engine, steps)
+    assert sorted(got) == sorted(want)
+    scale = max(float(np.abs(v).max()) for v in ref.values())
+    errs = all_errors(steps, got, want)
+    if dtype == "bfloat16":
+        ties = tied(name, requests)
+        kept = [e for e in errs if not ties[e[1]][e[2]]]
+        assert len(kept) >= 0.5 * len(errs), f"{len(errs) - len(kept)} of {len(errs)} places sit at a router's near tie"
+        errs = kept
+    bad = next((e for e in errs if not e[3] <= WORST[dtype] * scale), None)
+    assert bad is None, (f"first wrong place: step {bad[0]}, request {bad[1]}, position {bad[2]}, "
+                         f"error {bad[3]:.3e} > {WORST[dtype] * scale:.3e}")
+    over = [e for e in errs if not e[3] <= TOL[dtype] * scale]
+    assert len(over) <= share * len(errs), f"{len(over)} of {len(errs)} places beyond {TOL[dtype] * scale:.3e}; the first: {over[0]}"
+    assert engine.cache.n_requests() == 0
+    return got
+
+
+LENGTHS = {"A": [70, 45, 96, 33, 64, 51], "B": [5, 23, 40, 67, 90, 34], "C": [81, 40, 65, 97, 58], "D": [150, 47, 96, 201, 64],
+           "E": [130, 75, 40, 164]}
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", sorted(ALL))
+@pytest.mark.parametrize("family", ["whole", "tail", "portions", "mixed"])
+def test_family(name, dtype, family):
+    reqs = make_requests(name, LENGTHS[name])
+    steps = {"whole": traces.whole, "tail": traces.tail_one_by_one, "portions": traces.portions,
+             "mixed": lambda r: traces.mixed(r, seed=3)}[family](reqs)
+    check_trace(engine_for(name, dtype, steps), steps, name, reqs, dtype)
+    if family == "mixed":
+        assert traces.max_live_tokens(steps) < sum(traces.round_up(len(t), 64) for t in reqs.values())
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["A", "D"])
+def test_cutting_does_not_change_logits_beyond_rounding(name, dtype):
+    from tests.gpu_helpers import run_trace
+    reqs = make_requests(name, [61, 47, 75], seed=5)
+    outs = []
+    for build in (traces.whole, traces.tail_one_by_one, traces.portions, lambda r: traces.mixed(r, seed=9)):
+        steps = build(reqs)
+        got = run_trace(engine_for(name, dtype, steps), steps)
+        by_pos, at = {}, {}
+        for s in steps:
+            r = 0
+            for e in s["entries"]:
+                start = at.get(e["id"], 0)
+                for w in e["want"]:
+                    by_pos[(e["id"], start + w)] = got[s["step"]][r]
+                    r += 1
+                at[e["id"]] = start + len(e["tokens"])
+        outs.append(by_pos)
+    keys = set(outs[1]) & set(outs[0])
+    assert len(keys) > 90
+    scale = max(float(np.abs(v).max()) for v in outs[0].values())
+    tol = (2e-5 if dtype == "float32" else 0.2) * scale
+    for k in keys:
+        for o in outs[1:]:
+            if k in o:
+                assert np.abs(o[k] - outs[0][k]).max() <= tol, k
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["B", "D", "E"])
+def test_long_portions(name, dtype):
+    """Prompts of several hundred tokens, whole and in portions of 128 to 300 tokens beside another request's single
+    tokens: the recurrence runs in chunks side by side and the experts in tiles sorted by expert."""
+    reqs = make_requests(name, [700, 333], seed=13)
+    steps = traces.whole(reqs)
+    check_trace(engine_for(name, dtype, steps), steps, name, reqs, dtype)
+    a, b = reqs["r0"], reqs["r1"]
+    steps, at_a, at_b = [], 0, 0
+    steps.append({"step": 0, "entries": [{"id": "b", "tokens": b[:300], "want": [0, 150, 299]}], "end": []})
+    at_b = 300
+    for n in (300, 129, 200, 71):
+        steps.append({"step": len(steps), "entries": [{"id": "a", "tokens": a[at_a:at_a + n], "want": [0, n // 2, n - 1]},
+                                                     {"id": "b", "tokens": [b[at_b]], "want": [0]}],
+                      "end": ["a"] if at_a + n == 700 else []})
+        at_a += n
+        at_b += 1
+    steps.append({"step": len(steps), "entries": [{"id": "b", "tokens": b[at_b:], "want": [0, len(b) - at_b - 1]}], "end": ["b"]})
+    check_trace(engine_for(name, dtype, steps), steps, name, {"a": a, "b": b}, dtype)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["A", "C"])
+def test_long_decoding(name, dtype):
+    """390 tokens one by one: the cache grows over many pages, the recurrent state is carried through every step."""
+    reqs = make_requests(name, [400], seed=8)
+    steps = traces.tail_one_by_one(reqs, tail=390)
+    check_trace(engine_for(name, dtype, steps), steps, name, reqs, dtype)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["A", "B", "C"])
+def test_first_tokens_of_a_sequence(name, dtype):
+    reqs = make_requests(name, [1, 2, 3, 6], seed=11)
+    for build in (traces.whole, lambda r: traces.tail_one_by_one(r, tail=8)):
+        steps = build(reqs)
+        check_trace(engine_for(name, dtype, steps), steps, name, reqs, dtype, share=1.0 if dtype == "bfloat16" else 0.0)
+
+
+@pytest.mark.parametrize("name", ["A", "B"])
+def test_state_slots_and_pages_start_clean_when_used_again(name):
+    a = make_requests(name, [50], seed=20)
+    b = {"other": make_requests(name, [37], seed=21)["r0"]}
+    steps = traces.whole(a) + [dict(s, step=s["step"] + 1) for s in traces.portions(b, sizes=(1, 2, 3))]
+    eng = engine_for(name, "float32", steps, parallel=1)       # one slot: it must be reused
+    check_trace(eng, steps, name, dict(a, **b), "float32")
+
+
+# ---- each mechanism's kernel alone ------------------------------------------------------------------------------
+
+def _dev(a, dtype=None):
+    import torch
+    t = torch.as_tensor(np.ascontiguousarray(a)).cuda()
+    return t if dtype is None else t.to(dtype)
+
+
+def _bf16_round(a):
+    import torch
+    return torch.as_tensor(np.asarray(a, dtype=np.float32)).to(torch.bfloat16).float().numpy().astype(np.float64)
+
+
+def _attention_by_kernels(dtype, m, eps, rows, bias, cuts, page, v_other=None, lam=None):
+    """The prepared-head kernel and the general attention kernel on one request cut as `cuts`; rows: the 32-bit product
+    [T, q | k | v] before biases.  -> (attention output [T, heads*vdim], values as stored [T, kv*vdim])."""
+    import torch
+    from imparo_b200.kernels import ops
+    tdt = torch.float32 if dtype == "float32" else torch.bfloat16
+    nh, nkv, hd, vd = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
+    T = len(rows)
+    n_blocks = -(-T // page)
+    n_pages = n_blocks + 3
+    table = torch.arange(n_pages - 1, n_pages - 1 - n_blocks, -1, dtype=torch.int32, device="cuda").reshape(1, -1)
+    kc = torch.zeros(n_pages * page * nkv * hd, dtype=tdt, device="cuda")
+    vc = torch.zeros(n_pages * page * nkv * vd, dtype=tdt, device="cuda")
+    inv_freq, n_rot = None, 0
+    if m.get("rot"):
+        inv_freq, n_rot = _dev(P.rotation_frequencies(m["rot"]).astype(np.float32)), m["rot"]["dims"]
+    status = ops.new_status("cuda")
+    out_all, v_all = np.zeros((T, nh * vd)), np.zeros((T, nkv * vd))
+    at = 0
+    for n in cuts:
+        pos = _dev(np.arange(at, at + n, dtype=np.int32))
+        iot = _dev(np.zeros(n, dtype=np.int32))
+        q = torch.empty(n, nh * hd, dtype=tdt, device="cuda")
+        out = torch.empty(n, nh * vd, dtype=tdt, device="cuda")
+        v_save = torch.empty(n, nkv * vd, dtype=tdt, device="cuda")
+        other = None if v_other is None else _dev(v_other[at:at + n], tdt)
+        ops.qkv_prepare_store(_dev(rows[at:at + n], torch.float32), _dev(bias, torch.float32), pos, iot, inv_freq, n_rot, eps,
+                              other, None if lam is None else _dev(np.array([lam]), torch.float32), v_save, q, kc, vc, table,
+                              page, n_pages, nh, nkv, hd, vd, status)
+        ops.attention_any(q, kc, vc, pos, iot, table, page, n_pages, None, m["scale"], False, out, nh, nkv, hd, vd, status,
+                          softcap=m.get("softcap") or 0.0)
+        out_all[at:at + n] = out.float().cpu().numpy()
+        v_all[at:at + n] = v_save.float().cpu().numpy()
+        at += n
+    ops.read_status(status)
+    return out_all, v_all
+
+
+def _plain_attention_from_rows(m, eps, rows, bias, v_first=None, lam=None):
+    """The plain attention mixer fed with identity-like projections that pick q, k and v out of the row."""
+    nh, nkv, hd, vd = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
+    width = rows.shape[1]
+    eye = np.eye(width)
+    a, b = nh * hd, nh * hd + nkv * hd
+    W = {"q": eye[:a], "k": eye[a:b], "v": eye[b:], "q.b": bias[:a], "k.b": bias[a:b], "v.b": bias[b:], "o": np.eye(nh * vd),
+         "vmix": np.float64(lam if lam is not None else 0.0)}
+    return P.attention_mixer(rows, W, "", m, eps, v_first=v_first)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("nh,nkv,hd,vd,rot,cap,blend", [
+    (4, 2, 16, 24, {"dims": 8, "base": 300.0, "scaling": {"factor": 4.0, "low": 1.0, "high": 4.0, "original": 32}}, 5.0, True),
+    (6, 1, 24, 8, None, None, False),
+    (3, 3, 32, 32, {"dims": 32, "base": 500.0}, 30.0, True),
+    (8, 1, 96, 64, {"dims": 48, "base": 1e6, "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 64}}, 2.0, False),
+    (2, 1, 40, 200, {"dims": 6, "base": 20.0}, None, True)])
+def test_prepared_heads_and_capped_attention_kernels(dtype, nh, nkv, hd, vd, rot, cap, blend):
+    """Biases, rotation with rescaled frequencies, the norm without a weight, blended values and the soft cap: a prompt of
+    45 tokens, then 30 tokens one by one on the same cache (pages of 4: every border is crossed)."""
+    rng = np.random.default_rng(hd + vd)
+    T, eps = 75, 1e-5
+    m = {"heads": nh, "kv_heads": nkv, "dim": hd, "vdim": vd, "scale": 0.35}
+    if rot:
+        m["rot"] = rot
+    if cap:
+        m["softcap"] = cap
+    width = nh * hd + nkv * (hd + vd)
+    rows, bias = rng.standard_normal((T, width)), rng.standard_normal(width) * 0.5
+    v_other = rng.standard_normal((T, nkv, vd)) if blend else None
+    if dtype == "bfloat16" and blend:
+        v_other = _bf16_round(v_other)
+    lam = 0.3 if blend else None
+    want, want_v = _plain_attention_from_rows(m, eps, rows, bias, v_first=v_other, lam=lam)
+    got, got_v = _attention_by_kernels(dtype, m, eps, rows, bias, [45] + [1] * 30, 4,
+                                       v_other=None if v_other is None else v_other.reshape(T, -1), lam=lam)
+    tol = 2e-5 if dtype == "float32" else 2.5e-2
+    assert np.abs(got - want).max() <= tol * np.abs(want).max()
+    own_v = (rows + bias)[:, nh * hd + nkv * hd:]
+    assert np.abs(got_v - own_v).max() <= tol * np.abs(own_v).max()           # what is left for later layers is unblended
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("far,page", [(0, 16), (15, 16), (16, 16), (3, 4), (31, 8)])
+def test_a_far_key_among_hundreds_stands_out(dtype, far, page):
+    """Keys and queries are unit vectors after the norm, so a random key scores about 0 and the one key that points the
+    query's way scores scale * dim: with scale * dim = 14 it outweighs 600 others, and the output is its value.  The key
+    sits at the start of the sequence, at and around page borders; queries come in a prompt and decoded one by one."""
+    rng = np.random.default_rng(far + page)
+    nh, nkv, hd, vd, T = 2, 1, 32, 16, 620
+    m = {"heads": nh, "kv_heads": nkv, "dim": hd, "vdim": vd, "scale": 14.0 / hd, "softcap": 50.0}
+    width = nh * hd + nkv * (hd + vd)
+    rows = rng.standard_normal((T, width))
+    direction = rng.standard_normal(hd)
+    rows[far, nh * hd:nh * hd + hd] = direction                       # the marked key
+    rows[far, nh * hd + hd:] = 5.0                                    # its value
+    for t in (far + 1, 300, 599, 600, 619):
+        if t < T and t != far:
+            rows[t, :hd] = direction                                  # queries of head 0 that look for it
+    want, _ = _plain_attention_from_rows(m, 1e-5, rows, np.zeros(width))
+    assert abs(want[599, 0] - 5.0) < 0.1 and abs(want[300, 0] - 5.0) < 0.1        # the plain implementation does see it
+    assert abs(want[301, 0]) < 2.5                                    # and a query that does not look for it does not
+    got, _ = _attention_by_kernels(dtype, m, 1e-5, rows, np.zeros(width), [600] + [1] * 20, page)
+    assert np.abs(got - want).max() <= (2e-5 if dtype == "float32" else 3e-2) * np.abs(want).max()
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("heads,vdim,N,groups,taps,norm_groups", [(4, 8, 16, 2, 4, 2), (3, 32, 8, 3, 2, 1), (5, 12, 20, 1, 5, 5),
+                                                                  (2, 64, 128, 1, 3, 2), (4, 40, 64, 4, 1, 1), (1, 33, 200, 1, 7, 3)])
+def test_state_space_kernels(dtype, heads, vdim, N, groups, taps, norm_groups):
+    """Three requests of unequal length in one launch, then their next portions and single tokens from the states the
+    first launch left, slots in no particular order; conv, step sizes, recurrence (row by row and in chunks) and the
+    gated norm against the plain functions on each whole sequence."""
+    import torch
+    from imparo_b200.kernels import ops
+    tdt = torch.float32 if dtype == "float32" else torch.bfloat16
+    rng = np.random.default_rng(heads * 7 + N)
+    inner = heads * vdim
+    channels = inner + 2 * groups * N
+    d_in = 2 * inner + 2 * groups * N + heads
+    lens = [37, 5, 64 + 75 + 130]
+    rows = [rng.standard_normal((n, d_in)) * 0.7 for n in lens]
+    cw, cb = rng.standard_normal((channels, taps)) * 0.4, rng.standard_normal(channels) * 0.2
+    dt_bias, A_log, D = rng.uniform(-3, -0.5, heads), rng.uniform(-1.5, 1.0, heads), rng.uniform(0.5, 1.5, heads)
+    w_norm = rng.uniform(0.5, 1.5, inner)
+    eps = 1e-5
+    want = []
+    for r in rows:
+        T = len(r)
+        xbc = P.causal_conv_silu(r[:, inner:inner + channels], cw, cb)
+        dt = P.softplus(r[:, inner + channels:] + dt_bias)
+        y = P.selective_scan(xbc[:, :inner].reshape(T, heads, vdim), xbc[:, inner:inner + groups * N].reshape(T, groups, N),
+                             xbc[:, inner + groups * N:].reshape(T, groups, N), dt, A_log, D, groups).reshape(T, inner)
+        want.append(P.grouped_unit_rms(y * P.silu(r[:, :inner]), norm_groups, eps) * w_norm)
+    slots = [4, 0, 2]
+    ssm = torch.full((6, heads, N, vdim), 7.0, device="cuda")                        # stale values in every slot
+    conv = torch.full((6, max(taps - 1, 1), channels), 7.0, device="cuda")
+    ssm[slots] = 0.0
+    conv[slots] = 0.0
+    status = ops.new_status("cuda")
+    f32 = lambda a: _dev(np.asarray(a, dtype=np.float32))
+    got = [np.zeros_like(w) for w in want]
+    at = [0, 0, 0]
+    for cut in ([20, 2, 31], [16, 1, 2], [1, 1, 1], [0, 1, 30 + 75 + 130]):
+        items = [i for i in range(3) if cut[i]]
+        x = np.concatenate([rows[i][at[i]:at[i] + cut[i]] for i in items])
+        starts = np.concatenate([[0], np.cumsum([cut[i] for i in items])]).astype(np.int32)
+        iot = np.concatenate([np.full(cut[i], k, dtype=np.int32) for k, i in enumerate(items)])
+        T = len(x)
+        proj = f32(x)
+        xbc = torch.empty(T, channels, device="cuda")
+        dt = torch.empty(T, heads, device="cuda")
+        ops.mamba2_conv(proj, inner, inner + channels, channels, heads, taps, f32(cw), f32(cb), f32(dt_bias), conv, _dev(starts),
+                        _dev(iot), _dev(np.array([slots[i] for i in items], dtype=np.int32)), len(items), xbc, dt, status)
+        y = torch.empty(T, inner, device="cuda")
+        chunk, scratch = 0, None
+        if max(cut) >= 128:
+            chunk = 64
+            most = T // chunk + len(items)
+            scratch = (torch.empty(3 * most + len(items) + 1, dtype=torch.int32, device="cuda"),
+                       torch.empty(most * heads * N * vdim, device="cuda"), torch.empty(most * heads, device="cuda"))
+        ops.mamba2_scan(xbc, dt, f32(A_log), f32(D), ssm, _dev(starts), _dev(np.array([slots[i] for i in items], dtype=np.int32)),
+                        len(items), y, heads, vdim, N, groups, status, chunk=chunk, scratch=scratch)
+        out = torch.empty(T, inner, dtype=tdt, device="cuda")
+        ops.gate_group_rmsnorm(y, proj[:, :inner], f32(w_norm), eps, norm_groups, out)
+        o = out.float().cpu().numpy()
+        for k, i in enumerate(items):
+            got[i][at[i]:at[i] + cut[i]] = o[starts[k]:starts[k + 1]]
+            at[i] += cut[i]
+    ops.read_status(status)
+    assert float(ssm[1].min()) == 7.0 and float(conv[5].max()) == 7.0                # other slots untouched
+    for g, w in zip(got, want):
+        assert np.abs(g - w).max() <= (3e-5 if dtype == "float32" else 1e-2) * np.abs(w).max()
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("width,ff,experts,top,rows", [(64, 40, 6, 2, 5), (96, 64, 5, 1, 90), (100, 30, 3, 3, 33), (128, 64, 8, 2, 300),
+                                                       (72, 50, 7, 2, 1)])
+def test_routed_expert_kernels(dtype, width, ff, experts, top, rows):
+    """Router, choice and the experts, pair by pair and sorted into tiles, against the plain routed feed-forward."""
+    import torch
+    from imparo_b200.kernels import ops
+    tdt = torch.float32 if dtype == "float32" else torch.bfloat16
+    rng = np.random.default_rng(width + rows)
+    rnd = (lambda a: _bf16_round(a)) if dtype == "bfloat16" else (lambda a: a)
+    h = rnd(rng.standard_normal((rows, width)))
+    W = {"router": rng.standard_normal((experts, width)) * 0.3}
+    for e in range(experts):
+        W[f"e{e}.gate"], W[f"e{e}.up"], W[f"e{e}.down"] = (rnd(rng.standard_normal(s) * 0.15) for s in ((ff, width), (ff, width), (width, ff)))
+    mlp = {"router": {"experts": experts, "top": top}}
+    want = P.routed_experts(h, W, "", mlp)
+    scores = P.sigmoid(h @ W["router"].T)
+    ids = torch.empty(rows, top, dtype=torch.int32, device="cuda")
+    wts = torch.empty(rows, top, dtype=torch.float32, device="cuda")
+    hd = _dev(h, tdt)
+    ops.moe_route(hd, _dev(W["router"], torch.float32), top, ids, wts)
+    order = np.argsort(-scores, axis=1, kind="stable")[:, :top]
+    gap = np.sort(scores, axis=1)[:, -top] - (np.sort(scores, axis=1)[:, -top - 1] if top < experts else -1.0)
+    sure = gap > 1e-4                                                  # rows whose choice does not hang on a close call
+    assert sure.mean() > 0.9
+    assert (np.sort(ids.cpu().numpy()[sure], axis=1) == np.sort(order[sure], axis=1)).all()
+    assert np.abs(wts.cpu().numpy()[sure] - np.take_along_axis(scores, ids.cpu().numpy().astype(np.int64), 1)[sure]).max() < 1e-5
+    w_gu = _dev(np.stack([np.concatenate([W[f"e{e}.gate"], W[f"e{e}.up"]]) for e in range(experts)]), tdt)
+    w_down = _dev(np.stack([W[f"e{e}.down"] for e in range(experts)]), tdt)
+    pairs = rows * top
+    for grouped in (False, True):
+        mid = torch.empty(pairs, ff, dtype=tdt, device="cuda")
+        out = torch.full((rows, width), 9.0, device="cuda")
+        scratch = None
+        if grouped:
+            scratch = (torch.empty(pairs, width, device="cuda"),
+                       torch.empty(pairs + experts + 2 + 3 * (pairs // 32 + experts), dtype=torch.int32, device="cuda"))
+        ops.moe_experts(hd, w_gu, w_down, ids, wts, top, True, mid, out, scratch=scratch)
+        got = out.cpu().numpy()
+        assert np.abs(got - want)[sure].max() <= (3e-5 if dtype == "float32" else 2e-2) * np.abs(want).max(), grouped
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_output_norm_add_and_scale_kernels(dtype):
+    import torch
+    from imparo_b200.kernels import ops
+    rng = np.random.default_rng(3)
+    for rows, width in ((5, 64), (33, 100), (300, 256)):
+        x, y, w = rng.standard_normal((rows, width)), rng.standard_normal((rows, width)) * 3, rng.uniform(-0.3, 0.3, width)
+        want = x + P.offset_norm(y, w, 1e-5)
+        xd = _dev(x, torch.float32)
+        copy = torch.empty(rows, width, dtype=torch.float32 if dtype == "float32" else torch.bfloat16, device="cuda")
+        ops.out_norm_add(xd, _dev(y, torch.float32), _dev(1.0 + w, torch.float32), 1e-5, copy=copy)
+        assert np.abs(xd.cpu().numpy() - want).max() <= 1e-5
+        assert np.abs(copy.float().cpu().numpy() - want).max() <= (1e-5 if dtype == "float32" else 2e-2)
+        ops.scale_rows(xd, 1.5)
+        assert np.abs(xd.cpu().numpy() - 1.5 * want).max() <= 2e-5
+
+
+# ---- a far token and the state; generation through the framework's entry points ------------------------------------
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_a_far_token_is_carried_by_the_state(tmp_path, dtype):
+    """One state-space layer whose decay is close to 1 (A_log = -9) and nothing else that looks back: a marked token 0
+    of a 300-token prompt changes the last logits in the plain implementation, and the engine follows both variants,
+    whole, in portions (also longer than a chunk) and decoded one by one."""
+    from imparo_b200.engine import Engine
+    from imparo_b200.weights import write_random_model
+    cfg = {"architecture": "Negotar", "vocab": 64, "width": 48, "norm": {"eps": 1e-5},
+           "layers": [{"type": "mamba2", "mixer": {"heads": 2, "vdim": 24, "state": 16, "groups": 1, "conv": 2, "norm_groups": 1},
+                       "mlp": None}]}
+    d = str(tmp_path / "m")
+    write_random_model(d, cfg, seed=5, dtype="bfloat16", matrix_std=0.3, norm_jitter=0.2)
+    marked = read_safetensors(os.path.join(d, "model.safetensors"))["embed"].copy()
+    marked[63] *= 8.0                                   # a token that weighs in the state like sixty-four others
+    rescale(os.path.join(d, "model.safetensors"), {"l0.mix.A_log": np.full(2, -9.0, dtype=np.float32),
+                                                   "l0.mix.dt_bias": np.full(2, 0.5, dtype=np.float32), "embed": marked})
+    w = read_safetensors(os.path.join(d, "model.safetensors"))
+    rng = np.random.default_rng(1)
+    other = rng.integers(0, 62, 300).tolist()
+    base = [63] + other[1:]
+    reqs = {"a": base, "b": other}
+    ref = {k: P.forward(cfg, w, t) for k, t in reqs.items()}
+    scale = float(np.abs(ref["a"][1:]).max())
+    assert np.abs(ref["a"][-1] - ref["b"][-1]).max() > 0.01 * scale              # the far token does show at the end
+    for build in (traces.whole, lambda r: traces.portions(r, sizes=(64, 2, 33, 1, 1, 150)), lambda r: traces.tail_one_by_one(r, tail=40)):
+        steps = build(reqs)
+        eng = Engine(d, dtype=dtype, ctx=320, parallel=2, page_size=16, num_pages=40, max_step_tokens=320)
+        from tests.gpu_helpers import run_trace
+        got = run_trace(eng, steps)
+        want = traces.expected(steps, ref)
+        errs = [e for e in all_errors(steps, got, want) if e[2] > 0]
+        assert max(e[3] for e in errs) <= (3e-5 if dtype == "float32" else 4e-2) * scale
+
+
+def plain_generate(name, prompt, n_new):
+    toks, out, margins = list(prompt), [], []
+    for _ in range(n_new):
+        row = plain_logits(name, {"g": toks})["g"][-1]
+        t = int(np.argmax(row))
+        top2 = np.partition(row, -2)[-2:]
+        out.append(t)
+        margins.append(float(top2[1] - top2[0]))
+        toks.append(t)
+    return out, margins
+
+
+@pytest.mark.parametrize("dtype,min_margin", [("float32", 5e-3), ("bfloat16", 6.0)])       # logits reach 50 to 150 here
+@pytest.mark.parametrize("name", ["A", "B", "D"])
+def test_greedy_generation_through_the_scheduler(name, dtype, min_margin):
+    """Three prompts through Engine.generate: continuous batching with prompt portions of at most 8 tokens beside
+    decoding requests, two state slots for three requests, pages used again."""
+    from imparo_b200.engine import Engine
+    from tests.test_generate_gpu import agree
+    prompts = list(make_requests(name, [5, 23, 40], seed=1).values())
+    page = PAGE[name]
+    eng = Engine(model_dir(name), dtype=dtype, ctx=64, parallel=2, page_size=page, num_pages=2 * (64 // page), max_step_tokens=8)
+    got = eng.generate(prompts, max_tokens=10)
+    for i, p in enumerate(prompts):
+        want, margins = plain_generate(name, p, 10)
+        agree(got[i], want, margins, min_margin)
+    assert eng.cache.n_requests() == 0
+    eng.cache.check()
+
+
+def test_command_line_and_trace_runner(tmp_path):
+    from tests.test_trace_run_gpu import replay
+    name = "A"
+    prompt = make_requests(name, [16], seed=0)["r0"]
+    want, _ = plain_generate(name, prompt, 6)
+    tf = tmp_path / "tokens.txt"
+    tf.write_text(" ".join(map(str, prompt)))
+    r = subprocess.run([sys.executable, "-m", "imparo_b200", "-m", model_dir(name), "--dtype", "float32", "--decode", "6",
+                        "-c", "64", "-t", str(tf), "--json"], cwd=ROOT, capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stderr[-2000:]
+    assert json.loads(r.stdout.strip().splitlines()[-1])["tokens"] == [want]
+    reqs = make_requests(name, [70, 33, 90, 41, 64, 52], seed=7)
+    steps = traces.mixed(reqs, seed=1)
+    max_tokens = traces.max_live_tokens(steps, 64)
+    out = tmp_path / "out"
+    replay(model_dir(name), "bfloat16", steps, out, max_tokens)
+    ref = plain_logits(name, reqs)
+    want = traces.expected(steps, ref)
+    got = {s["step"]: np.fromfile(out / f"{s['step']}.f32", dtype="<f4").reshape(-1, ALL[name]["vocab"]) for s in steps if s["step"] in want}
+    scale = max(float(np.abs(v).max()) for v in ref.values())
+    errs = all_errors(steps, got, want)
+    assert max(e[3] for e in errs) <= WORST["bfloat16"] * scale
+    assert sum(e[3] > TOL["bfloat16"] * scale for e in errs) <= 0.1 * len(errs)
