@@ -20,7 +20,7 @@ captured for its shape, as every step whose shape repeats is.
 --workload continuous | long run the baseline's two other workloads (LFM2-700M sizes under
 continuous batching; LFM2-350M sizes with 32,768-token prompts in bfloat16 and 32-bit) and
 print one JSON line each; --workload sizes runs the headline's model at further prompt lengths
-and decode contexts; --workload vipotar runs the Vipotar design at two sizes that resemble a real model's layers beside
+and decode contexts; --workload vipotar / negotar run the Vipotar / Negotar design at two sizes that resemble a real model's layers beside
 LFM2 at equal width, depth, heads and feed-forward size (prefill of one prompt, decode at batch 8); the default is the
 headline above.
 """
@@ -333,6 +333,98 @@ def workload_vipotar(args):
     return 0
 
 
+def negotar_config(width, layers, heads, kv_heads, head, ssm_heads, ssm_vdim, ssm_state, experts, top, ff, vocab):
+    """A Negotar config.json of the given sizes: attention and state-space layers in turn (the first an attention layer),
+    every head rotated with rescaled frequencies, scores capped at 30, values shared from the first attention layer,
+    `experts` experts of `ff` features of which a token uses `top`."""
+    attn = {"heads": heads, "kv_heads": kv_heads, "dim": head, "vdim": head, "scale": head ** -0.5 * 8.0, "softcap": 30.0,
+            "v_mix": True, "rot": {"dims": head, "base": 500000.0, "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 2048}}}
+    ssm = {"heads": ssm_heads, "vdim": ssm_vdim, "state": ssm_state, "groups": 1, "conv": 4, "norm_groups": 1}
+    mlp = {"kind": "moe", "router": {"experts": experts, "top": top}, "expert": {"ff": ff}}
+    return {"architecture": "Negotar", "vocab": vocab, "width": width, "norm": {"eps": 1e-5}, "logit_scale": 1.0,
+            "layers": [{"type": "attention" if i % 2 == 0 else "mamba2", "mixer": attn if i % 2 == 0 else ssm, "mlp": mlp}
+                       for i in range(layers)]}
+
+
+def workload_negotar(args):
+    """Negotar at two sizes beside LFM2 at equal width, depth, heads and active feed-forward size (top * ff): prefill of one
+    prompt of 512 and 2,048 tokens, decode steps of 8 requests with 2,048 positions each.  Rooflines: prefill against the
+    measured bfloat16 peak with the flops the design needs (products over all tokens, experts over the tokens that use
+    them, causal attention, the recurrence's 6 * heads * state * vdim per token); decode against the measured copy
+    bandwidth with the bytes a step must move (every dense matrix once, the experts the step's rows can reach at most,
+    the keys and values, the recurrent states read and written)."""
+    import numpy as np
+    import torch
+    from imparo_b200.engine import Engine
+    rng = np.random.default_rng(0)
+    pk = peaks()
+    sizes = {"width1024": dict(width=1024, layers=8, heads=16, kv_heads=4, head=64, ssm_heads=32, ssm_vdim=64, ssm_state=64,
+                               experts=16, top=2, ff=1024, vocab=32768),
+             "width2048": dict(width=2048, layers=8, heads=32, kv_heads=8, head=64, ssm_heads=64, ssm_vdim=64, ssm_state=128,
+                               experts=32, top=4, ff=1024, vocab=65536)}
+    out = {"metric": "Negotar beside LFM2 at equal sizes: prefill of one prompt, decode at batch 8 with 2,048 positions",
+           "unit": "tokens/s", "dtype": "bf16", "data": "synthetic (random weights, uniform-random token ids)", "sizes": {}}
+    with ClockSampler() as clocks:
+        for name, z in sizes.items():
+            row = {}
+            W, L, V = z["width"], z["layers"], z["vocab"]
+            F = z["top"] * z["ff"]
+            for model in ("negotar", "lfm2"):
+                if model == "negotar":
+                    cfg = negotar_config(**z)
+                    n_attn = (L + 1) // 2
+                    n_ssm = L - n_attn
+                    inner, N = z["ssm_heads"] * z["ssm_vdim"], z["ssm_state"]
+                    attn = (z["heads"] + 2 * z["kv_heads"]) * z["head"] * W + W * z["heads"] * z["head"]
+                    ssm = (2 * inner + 2 * N + z["ssm_heads"]) * W + W * inner
+                    expert = 3 * W * z["ff"]
+                    dense = n_attn * attn + n_ssm * ssm + L * z["experts"] * W
+                    state = n_ssm * z["ssm_heads"] * N * z["ssm_vdim"] * 4
+                    kv_tok = n_attn * 2 * z["kv_heads"] * z["head"] * 2
+                    params = dense + L * z["experts"] * expert + V * W
+
+                    def flops(T):
+                        return (2.0 * T * (dense + L * z["top"] * expert) + 2.0 * V * W
+                                + n_attn * 4.0 * z["heads"] * z["head"] * T * (T + 1) / 2 + n_ssm * 6.0 * inner * N * T)
+
+                    def step_bytes(batch, ctx):
+                        reached = min(z["experts"], batch * z["top"])
+                        return (dense + L * reached * expert + V * W) * 2 + batch * (2 * state + ctx * kv_tok)
+                else:
+                    cfg = lfm2_like(W, L, z["heads"], z["kv_heads"], z["head"], F, V)
+                    n_attn = sum(1 for t in cfg["layer_types"] if t != "conv")
+                    attn = (z["heads"] + 2 * z["kv_heads"]) * z["head"] * W + W * z["heads"] * z["head"]
+                    matrix = L * 3 * W * F + (L - n_attn) * 4 * W * W + n_attn * attn
+                    kv_tok = n_attn * 2 * z["kv_heads"] * z["head"] * 2
+                    params = matrix + V * W
+
+                    def flops(T):
+                        return 2.0 * T * matrix + 2.0 * V * W + n_attn * 4.0 * z["heads"] * z["head"] * T * (T + 1) / 2
+
+                    def step_bytes(batch, ctx):
+                        return (matrix + V * W) * 2 + batch * ctx * kv_tok
+                engine = Engine(config=cfg, seed=0, dtype="bfloat16", ctx=CTX, parallel=8, page_size=PAGE, max_step_tokens=PROMPT,
+                                random_init={"norm_jitter": 0.0})
+                r = {"params": params, "prefill": {}}
+                for T in (512, 2048):
+                    ms = measure_prefill(engine, reps=5, warmup=3, rng=rng, prompt=T)
+                    r["prefill"][str(T)] = {"value": round(T * 1000.0 / ms, 1), "ms": round(ms, 3),
+                                            "frac": round(flops(T) / (ms * 1e-3) / (pk["bf16_tflops_burst"] * 1e12), 4)}
+                ms, launches, library, ctx = measure_decode(engine, 8, max(20, args.steps // 4), max(args.warmup, 3), rng, prompt=PROMPT)
+                nbytes = step_bytes(8, ctx)
+                r["decode_b8"] = {"value": round(8 * 1000.0 / ms, 1), "ms_per_step": round(ms, 4), "own_kernels_per_step": round(launches, 1),
+                                  "library_gemms_per_step": round(library, 1), "bytes_per_step": int(nbytes),
+                                  "frac": round(nbytes / (ms * 1e-3) / 1e9 / pk["hbm_gbs"], 4)}
+                row[model] = r
+                del engine
+                torch.cuda.empty_cache()
+            out["sizes"][name] = dict(row, config=z)
+    out["peaks"] = pk["source"]
+    out["clocks"] = clocks.summary()
+    print(json.dumps(out))
+    return 0
+
+
 def _preset(name):
     with open(os.path.join(ROOT, "imparo_b200", "config", "presets", name + ".json")) as f:
         return json.load(f)
@@ -551,7 +643,7 @@ def main():
     ap.add_argument("--skip-points", action="store_true", help="skip the batch-1 and batch-64 points")
     ap.add_argument("--only-decode", action="store_true", help="time the decode steps only (for profiler captures)")
     ap.add_argument("--only-prefill", action="store_true", help="time the 2,048-token prompt only (for profiler captures)")
-    ap.add_argument("--workload", default="headline", choices=["headline", "continuous", "long", "sizes", "vipotar"],
+    ap.add_argument("--workload", default="headline", choices=["headline", "continuous", "long", "sizes", "vipotar", "negotar"],
                     help="headline (default): the line the contract names.  continuous: LFM2-700M sizes, requests with prompts "
                          "of 64 to 4,096 tokens through 32 slots in 512-token portions beside decode rows, temperature 0.7, 128 new "
                          "tokens each.  long: LFM2-350M sizes, 4 prompts of 32,768 tokens and 512 greedy tokens each, bfloat16 and 32-bit.  "
@@ -579,6 +671,8 @@ def main():
         return workload_sizes(args)
     if args.workload == "vipotar":
         return workload_vipotar(args)
+    if args.workload == "negotar":
+        return workload_negotar(args)
     cfg = dict(LFM2_1_2B)
     if args.layers is not None and args.layers < cfg["num_hidden_layers"]:
         cfg["layer_types"] = cfg["layer_types"][:args.layers]

@@ -296,6 +296,7 @@ struct QkvSource {
     float eps;
     __nv_bfloat16* k_out;       // the caches, writable
     __nv_bfloat16* v_out;
+    float softcap;              // c > 0: the scaled score becomes c * tanh(score / c) (with or without the fields above)
 };
 
 template <int HD, bool FROM_QKV>
@@ -532,6 +533,17 @@ attn_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16*
         }
         const int key0 = kb * KEYS + warp * 16 + 2 * tg;
         const int wk0 = kb * KEYS + warp * 16;
+        if (src.softcap > 0.f) {                                // raw products become (c / scale) tanh(raw * scale / c)
+            const float cin = scale / src.softcap, cout = src.softcap / scale;
+#pragma unroll
+            for (int n = 0; n < 2; ++n)
+#pragma unroll
+                for (int e = 0; e < 2; ++e) {
+                    float y;
+                    asm("tanh.approx.f32 %0, %1;" : "=f"(y) : "f"(s[n][e] * cin));
+                    s[n][e] = cout * y;
+                }
+        }
         float mx = -INFINITY;
         if (wk0 >= begin && wk0 + 16 <= end) {                  // all 16 keys are live: no masks
 #pragma unroll
@@ -673,7 +685,7 @@ static int decode_mma_launch(const void* q, const pf::QkvSource* qkv_src, const 
                              const int* table, int max_blocks, int page_size, int n_pages,
                              int window, float scale, void* out, float* part_acc, float* part_ml,
                              int n_tok, int nh, int nkv, int hd, int chunk, int n_splits, int fresh, int overlap_prev,
-                             int* status, cudaStream_t stream) {
+                             int* status, cudaStream_t stream, float softcap = 0.f) {
     if (n_tok <= 0) return 0;
     if (nkv <= 0 || nh % nkv != 0) return -5;
     if (nh / nkv > 8 || (hd != 64 && hd != 128)) return -8;
@@ -695,7 +707,8 @@ static int decode_mma_launch(const void* q, const pf::QkvSource* qkv_src, const 
         configured = true;
     }
     const bool from_qkv = qkv_src != nullptr;
-    const pf::QkvSource none{};
+    pf::QkvSource none{};
+    none.softcap = softcap > 0.f ? softcap : 0.f;
     const pf::QkvSource& src = from_qkv ? *qkv_src : none;
 #define IMPARO_DECODE(HD_, F_) launch(pf::attn_decode_mma_kernel<HD_, F_>, grid, dim3(pf::THREADS), smem, stream, \
         (const __nv_bfloat16*)q, (const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache, positions, item_of_token, table, \
@@ -713,10 +726,10 @@ extern "C" int imparo_attention_decode_mma(const void* q, const void* k_cache, c
                                            const int* table, int max_blocks, int page_size, int n_pages,
                                            int window, float scale, void* out, float* part_acc, float* part_ml,
                                            int n_tok, int nh, int nkv, int hd, int chunk, int n_splits, int fresh,
-                                           int overlap_prev, int* status, cudaStream_t stream) {
+                                           int overlap_prev, float softcap, int* status, cudaStream_t stream) {
     return decode_mma_launch(q, nullptr, k_cache, v_cache, positions, item_of_token, table, max_blocks, page_size, n_pages, window,
                              scale, out, part_acc, part_ml, n_tok, nh, nkv, hd, chunk, n_splits, fresh, overlap_prev ? 1 : 0,
-                             status, stream);
+                             status, stream, softcap);
 }
 
 // The same for a step in which every request brings ONE token, straight from the qkv product's split partials

@@ -76,6 +76,14 @@ __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
     return *reinterpret_cast<uint32_t*>(&v);
 }
 
+// tanh by its approximate instruction (2^-11 of the result): the capped scores feed probabilities that are rounded to
+// bfloat16 anyway
+__device__ __forceinline__ float tanh_fast(float x) {
+    float y;
+    asm("tanh.approx.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
 struct Args {
     const __nv_bfloat16* q;
     __nv_bfloat16* out;
@@ -88,6 +96,9 @@ struct Args {
     int late_trigger;        // the next kernel runs beside this one and must find all before this one complete (common.cuh)
     int sink;                // the softmax's denominator counts one more term of score 0 that has no value: the running max
                              // starts at 0 and the running sum at 1, as if a key of score 0 had been seen before all others
+    float softcap;           // c > 0: the scaled score becomes c * tanh(score / c).  The raw product v is replaced by
+                             // (c / scale) * tanh(v * scale / c) as soon as it is read, so that everything after it (the
+                             // max, which commutes with a rising function, and the exponent) stays as it is
 };
 
 template <int HD>
@@ -283,6 +294,8 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
         for (int d = 0; d < DH; ++d) o[d] = 0.f;
         float m_run = a.sink ? 0.f : -INFINITY, l_run = (a.sink && half == 0) ? 1.f : 0.f, corr_prev = 0.f;
         const float sl2 = a.scale * 1.4426950408889634f;     // scores in units of log2(e)
+        const bool capped = a.softcap > 0.f;
+        const float cap_in = capped ? a.scale / a.softcap : 0.f, cap_out = capped ? a.softcap / a.scale : 0.f;
         bool ok = true;
         auto fold_pv = [&](float corr) {                     // o = o * corr + O_step (this thread's dims)
 #pragma unroll
@@ -336,7 +349,9 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
             if (*gave_up) { ok = false; break; }
             float mx_a, mx_b;
             tmem_ld2(t_x, mx_a, mx_b);
-            const float mx = fmaxf(mx_a, mx_b) * sl2;        // sl2 > 0: the max commutes with the scaling
+            float mx_raw = fmaxf(mx_a, mx_b);
+            if (capped && mx_raw != -INFINITY) mx_raw = cap_out * tanh_fast(mx_raw * cap_in);
+            const float mx = mx_raw * sl2;                   // sl2 > 0: the max commutes with the scaling
             const float m_new = fmaxf(m_run, mx);
             const float corr = (m_run == -INFINITY) ? 0.f : ex2(m_run - m_new);
             const float base = (m_new == -INFINITY) ? 0.f : m_new;
@@ -354,6 +369,12 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
             for (int h = 0; h < 2; ++h) {
                 float v[2][16];
                 tmem_ld_chunks<2>(t_s + h * 32, v);
+                if (capped) {
+#pragma unroll
+                    for (int u = 0; u < 2; ++u)
+#pragma unroll
+                        for (int e = 0; e < 16; ++e) v[u][e] = cap_out * tanh_fast(v[u][e] * cap_in);
+                }
 #pragma unroll
                 for (int u = 0; u < 2; ++u) {
                     uint32_t w[8];
@@ -751,6 +772,8 @@ attn_prefill_pp_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
         }
         float m_used = -INFINITY, l_run = (a.sink && half == 0) ? 1.f : 0.f;       // (the sink's 1 is in units of max 0: see j == 0)
         const float sl2 = a.scale * 1.4426950408889634f;     // scores in units of log2(e)
+        const bool capped = a.softcap > 0.f;
+        const float cap_in = capped ? a.scale / a.softcap : 0.f, cap_out = capped ? a.softcap / a.scale : 0.f;
         bool ok = true;
         uint8_t* prow = p_s + x * P_BYTES + half * REGION + r * 128;         // keys 0-63 and 64-127 are the two blocks of P
         for (int j = 0; j < n_x; ++j) {
@@ -763,6 +786,13 @@ attn_prefill_pp_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
             keep32(sv[0]); keep32(sv[1]);
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
             mbar_arrive(&s_free[x]);                         // the score columns may take the next step's product
+            if (capped) {
+#pragma unroll
+                for (int q2 = 0; q2 < 2; ++q2)
+#pragma unroll
+                    for (int e = 0; e < 32; ++e)
+                        sv[q2][e] = __float_as_uint(cap_out * tanh_fast(__uint_as_float(sv[q2][e]) * cap_in));
+            }
             const int key0 = (kb_first + j) * KEYS + half * 64;              // this thread's first key of the step
             const int j_hi = valid ? min(63, pos_r - key0) : -1;             // the keys this row sees: [j_lo, j_hi]
             const int j_lo = max(0, lo_r - key0);
@@ -942,7 +972,7 @@ using namespace imparo;
 extern "C" int imparo_attention_prefill_tc(const void* q, const void* k_cache, const void* v_cache,
                                            const int* item_row_start, const int* item_start_pos, int n_items,
                                            const int* table, int max_blocks, int page_size, int n_pages,
-                                           int window, float scale, void* out, int n_tok, int nh, int nkv, int hd,
+                                           int window, float scale, float softcap, void* out, int n_tok, int nh, int nkv, int hd,
                                            int mode, int* status, cudaStream_t stream) {
     const int two_tiles = mode & 1;
     if (n_tok <= 0) return 0;
@@ -968,6 +998,7 @@ extern "C" int imparo_attention_prefill_tc(const void* q, const void* k_cache, c
     a.nh = nh; a.nkv = nkv; a.scale = scale;
     a.late_trigger = (mode >> 1) & 1;
     a.sink = (mode >> 2) & 1;
+    a.softcap = softcap > 0.f ? softcap : 0.f;
     if (hd == 64 && two_tiles) {
         // two tiles per CTA: half as many CTAs along y (an upper bound again)
         const long long pairs = (n_tok + 2 * TQ - 1) / (2 * TQ) + n_items;

@@ -18,6 +18,8 @@
 //       (imparo-cpu/src/ops.rs:73-78; imparo-model/src/lfm2/workflow_cpu.rs:307-313): the
 //       [T, 2F] intermediate and the activation kernel's pass over it disappear.
 // The reference hands these products to cuBLAS (imparo-cuda/native/bf16_bounded_gemm.cuh:4-28).
+//   * Grouped: token tiles that each belong to one of several stacked matrices (rows sorted by group, every group's rows
+//     starting at a multiple of 128), named by a device table; tiles without rows are skipped by all roles alike.
 //
 // Every wait on an mbarrier is bounded: when one runs out the kernel records
 // IMPARO_ST_WAIT_LIMIT in the status word, stops waiting, frees its tensor memory and returns.
@@ -44,6 +46,12 @@ struct Params {
     int T, N, K, ldo;        // N = output columns (SwiGLU: F, W has 2F rows)
     int kblocks;             // ceil(K / BK)
     int m_tiles, n_tiles;
+    // Grouped products (one matrix per group of token tiles, e.g. the experts of a routed feed-forward): tile_group[tm]
+    // names the group of token tile tm, or -1 for a tile that holds no rows; W is the groups' matrices stacked, group_rows
+    // rows each.  The table is made on the device by an earlier kernel of the chain, so every role waits for that kernel
+    // before its first look at it, and all three skip the same tiles.  null: one matrix for all tiles.
+    const int* tile_group;
+    int group_rows;
 };
 
 __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
@@ -106,15 +114,16 @@ gemm_prefill_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
         if (lane == 0) {
             // W is written by no kernel: the first ring of W tiles is requested before the wait on
             // the previous kernel.  g counts k-blocks over all of this CTA's tiles.
+            int w_row0 = 0;                                  // first row of the tile's group in the stacked W
             auto load_w = [&](int g, int tn, int kb) {
                 const int s = g % STAGES;
                 uint8_t* b = smem + s * STAGE_BYTES + A_BYTES;
                 mbar_expect_tx(&full[s], STAGE_BYTES);
                 if (EPI == SWIGLU_BF16) {
-                    tma_load_2d(b, &map_w, &full[s], kb * BK, tn * 128);                      // 128 gate rows
-                    tma_load_2d(b + B_BYTES / 2, &map_w, &full[s], kb * BK, p.N + tn * 128);  // their 128 up rows
+                    tma_load_2d(b, &map_w, &full[s], kb * BK, w_row0 + tn * 128);                      // 128 gate rows
+                    tma_load_2d(b + B_BYTES / 2, &map_w, &full[s], kb * BK, w_row0 + p.N + tn * 128);  // their 128 up rows
                 } else {
-                    tma_load_2d(b, &map_w, &full[s], kb * BK, tn * TN);
+                    tma_load_2d(b, &map_w, &full[s], kb * BK, w_row0 + tn * TN);
                 }
             };
             auto load_x = [&](int g, int tm, int kb) {
@@ -124,9 +133,15 @@ gemm_prefill_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
             pdl_trigger();
             int g = 0;
             bool ok = true, first = true;
+            if (p.tile_group) { pdl_wait(); first = false; }
             for (int idx = blockIdx.x; idx < n_tiles_total && ok; idx += gridDim.x) {
                 int tm, tn;
                 tile_of(idx, p, tm, tn);
+                if (p.tile_group) {
+                    const int grp = p.tile_group[tm];
+                    if (grp < 0) continue;
+                    w_row0 = grp * p.group_rows;
+                }
                 int kb = 0;
                 if (first) {
                     const int early = p.kblocks < STAGES ? p.kblocks : STAGES;
@@ -153,9 +168,16 @@ gemm_prefill_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
         if (lane == 0) {
             const uint32_t idesc = instr_desc(TM, TN);
             const uint64_t desc_a0 = smem_desc(smem_u32(smem)), desc_b0 = smem_desc(smem_u32(smem) + A_BYTES);
-            int g = 0, it = 0;
+            int g = 0, it = -1;
             bool ok = true;
-            for (int idx = blockIdx.x; idx < n_tiles_total && ok; idx += gridDim.x, ++it) {
+            if (p.tile_group) pdl_wait();
+            for (int idx = blockIdx.x; idx < n_tiles_total && ok; idx += gridDim.x) {
+                if (p.tile_group) {
+                    int tm, tn;
+                    tile_of(idx, p, tm, tn);
+                    if (p.tile_group[tm] < 0) continue;
+                }
+                ++it;
                 const int b = it & 1, use = it >> 1;
                 if (use > 0 && !mbar_wait(&acc_empty[b], (use - 1) & 1)) {       // the epilogue has read this accumulator out
                     report(p.status, IMPARO_ST_WAIT_LIMIT, 21, idx, b);
@@ -188,10 +210,12 @@ gemm_prefill_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
         // ---- epilogue: warps 2..5 own tensor-memory lanes 32*(warp%4) .. +32; a lane is a token ----
         const int quad = warp & 3;
         pdl_wait();                                             // before any global write or residual read
-        int it = 0;
-        for (int idx = blockIdx.x; idx < n_tiles_total; idx += gridDim.x, ++it) {
+        int it = -1;
+        for (int idx = blockIdx.x; idx < n_tiles_total; idx += gridDim.x) {
             int tm, tn;
             tile_of(idx, p, tm, tn);
+            if (p.tile_group && p.tile_group[tm] < 0) continue;
+            ++it;
             const int b = it & 1, use = it >> 1;
             const bool ok = p.kblocks == 0 || mbar_wait(&acc_full[b], use & 1);
             if (!ok) {
@@ -374,6 +398,43 @@ extern "C" int imparo_gemm_prefill(const void* x, int ldx, int x_rows_alloc, con
         case STORE_BF16: return launch_prefill<STORE_BF16>(mw, mx, p, ctas, stream);
         case STORE_F32: return launch_prefill<STORE_F32>(mw, mx, p, ctas, stream);
         case ADD_F32: return launch_prefill<ADD_F32>(mw, mx, p, ctas, stream);
+        default: return launch_prefill<SWIGLU_BF16>(mw, mx, p, ctas, stream);
+    }
+}
+
+
+// The same product for rows that are sorted by group: x [rows, K] holds every group's rows from a multiple of 128 on
+// (rows = 128 * m_tiles, padding rows hold anything), w the groups' matrices stacked ([n_groups * N, K]; SwiGLU:
+// [n_groups * 2N, K], each group its gate rows then its up rows), tile_group int32 [m_tiles] on the device (-1: a tile
+// without rows).  epilogue: 0 store bfloat16, 1 store float32, 3 SwiGLU.  Refusals as above.
+extern "C" int imparo_gemm_prefill_grouped(const void* x, int ldx, const void* w, int n_groups, void* out, int ldo, int m_tiles,
+                                           int N, int K, int epilogue, const int* tile_group, int* status, cudaStream_t stream) {
+    if (m_tiles <= 0 || N <= 0 || n_groups <= 0) return 0;
+    if (K <= 0 || K % 8 != 0 || ldx % 8 != 0) return -23;
+    if (((uintptr_t)x | (uintptr_t)w | (uintptr_t)out) & 15) return -23;
+    if (epilogue != STORE_BF16 && epilogue != STORE_F32 && epilogue != SWIGLU_BF16) return -22;
+    const bool f32_out = epilogue == STORE_F32;
+    if (N % (f32_out ? 4 : 8) != 0 || ldo % (f32_out ? 4 : 8) != 0) return -23;
+    const int group_rows = epilogue == SWIGLU_BF16 ? 2 * N : N;
+    const int T = m_tiles * TM;
+    CUtensorMap mw, mx;
+    int rc = get_map(w, (uint64_t)n_groups * group_rows, (uint64_t)K, (uint64_t)K, epilogue == SWIGLU_BF16 ? 128u : (uint32_t)TN, &mw);
+    if (rc) return rc;
+    rc = get_map(x, (uint64_t)T, (uint64_t)K, (uint64_t)ldx, (uint32_t)TM, &mx);
+    if (rc) return rc;
+    Params p = {};
+    p.out = out; p.status = status;
+    p.T = T; p.N = N; p.K = K; p.ldo = ldo; p.kblocks = (K + BK - 1) / BK;
+    p.m_tiles = m_tiles;
+    p.n_tiles = epilogue == SWIGLU_BF16 ? (N + 127) / 128 : (N + TN - 1) / TN;
+    p.tile_group = tile_group;
+    p.group_rows = group_rows;
+    const long long tiles = (long long)p.m_tiles * p.n_tiles;
+    if (tiles > (1 << 30)) return -2;
+    const int ctas = (int)(tiles < sm_count() ? tiles : sm_count());
+    switch (epilogue) {
+        case STORE_BF16: return launch_prefill<STORE_BF16>(mw, mx, p, ctas, stream);
+        case STORE_F32: return launch_prefill<STORE_F32>(mw, mx, p, ctas, stream);
         default: return launch_prefill<SWIGLU_BF16>(mw, mx, p, ctas, stream);
     }
 }

@@ -24,21 +24,31 @@ template <typename T>
 __global__ void __launch_bounds__(128)
 moe_route_kernel(const T* __restrict__ h, const float* __restrict__ w_r, int n_rows, int width, int experts, int top,
                  int softmax_scores, int renormalise, int* __restrict__ ids, float* __restrict__ wts) {
-    extern __shared__ float route_smem[];
+    extern __shared__ float route_smem[];                // [width] the row in 32-bit, then [experts] logits
     pdl_trigger();
     pdl_wait();
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const int r = blockIdx.x * 4 + warp;
-    if (r >= n_rows) return;
-    float* s = route_smem + (size_t)warp * experts;
+    const int r = blockIdx.x;
+    float* row = route_smem;
+    float* s = route_smem + width;
     const T* hr = h + (size_t)r * width;
-    for (int e = 0; e < experts; ++e) {
+    for (int i = threadIdx.x; i < width; i += blockDim.x) row[i] = to_f32(hr[i]);
+    __syncthreads();
+    // a warp per expert in turn; the dot product always adds in the same order (four partial sums per lane, then the
+    // lanes), whatever else the launch holds
+    for (int e = warp; e < experts; e += 4) {
         const float* wr = w_r + (size_t)e * width;
-        float acc = 0.f;
-        for (int i = lane; i < width; i += 32) acc += wr[i] * to_f32(hr[i]);
-        acc = warp_sum(acc);
+        float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
+        int i = lane;
+        for (; i + 96 < width; i += 128) {
+            a0 += wr[i] * row[i]; a1 += wr[i + 32] * row[i + 32]; a2 += wr[i + 64] * row[i + 64]; a3 += wr[i + 96] * row[i + 96];
+        }
+        for (; i < width; i += 32) a0 += wr[i] * row[i];
+        const float acc = warp_sum((a0 + a1) + (a2 + a3));
         if (lane == 0) s[e] = acc;
     }
+    __syncthreads();
+    if (warp != 0) return;
     __syncwarp();
     // The choice goes by the logits: scores are monotone in them, and a sigmoid that has reached 1 in 32-bit would tie.
     float m = -INFINITY, l = 1.f;
@@ -352,6 +362,109 @@ moe_sum_pairs_kernel(const float* __restrict__ pair_out, int n_rows, int width, 
     }
 }
 
+// ---- (4) sorted into tiles of 128 rows for the tensor-memory product (gemm_prefill.cu, grouped) --------------------------
+// One block.  Every pair gets a row in a buffer in which each expert's rows start at a multiple of 128: slot_of_pair[p];
+// tile_group[t] names the expert of row tile t, -1 beyond the last used tile.  Inside an expert the rows keep the pairs'
+// order.  Shared memory: (32 + 2) * experts ints.
+constexpr int TILE_ROWS = 128;
+
+__global__ void __launch_bounds__(1024)
+moe_tile_plan_kernel(const int* __restrict__ ids, int n_pairs, int experts, int* __restrict__ slot_of_pair,
+                     int* __restrict__ tile_group, int max_tiles) {
+    extern __shared__ int tp_smem[];
+    int* warp_counts = tp_smem;                          // [32][experts]
+    int* base = tp_smem + 32 * experts;                  // [experts] pairs seen so far
+    int* start_row = base + experts;                     // [experts] first row of the expert's stretch
+    pdl_trigger();
+    pdl_wait();
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    for (int e = tid; e < experts; e += blockDim.x) base[e] = 0;
+    for (int p0 = 0; p0 < n_pairs; p0 += 1024) {
+        for (int i = tid; i < 32 * experts; i += blockDim.x) warp_counts[i] = 0;
+        __syncthreads();
+        const int p = p0 + tid;
+        int e = p < n_pairs ? ids[p] : -1;
+        if (e >= experts) e = -1;
+        const unsigned same = __match_any_sync(0xffffffffu, e);
+        const int rank = __popc(same & ((1u << lane) - 1u));
+        if (e >= 0 && rank == 0) warp_counts[warp * experts + e] = __popc(same);
+        __syncthreads();
+        for (int x = tid; x < experts; x += blockDim.x) {
+            int run = base[x];
+            for (int w = 0; w < 32; ++w) {
+                const int c = warp_counts[w * experts + x];
+                warp_counts[w * experts + x] = run;
+                run += c;
+            }
+            base[x] = run;
+        }
+        __syncthreads();
+        if (p < n_pairs) slot_of_pair[p] = e >= 0 ? warp_counts[warp * experts + e] + rank : -1;
+        __syncthreads();
+    }
+    if (tid == 0) {
+        int t = 0;
+        for (int e = 0; e < experts; ++e) {
+            start_row[e] = t * TILE_ROWS;
+            const int n = (base[e] + TILE_ROWS - 1) / TILE_ROWS;
+            for (int i = 0; i < n && t < max_tiles; ++i) tile_group[t++] = e;
+        }
+        for (; t < max_tiles; ++t) tile_group[t] = -1;
+    }
+    __syncthreads();
+    for (int p = tid; p < n_pairs; p += blockDim.x) {
+        const int e = ids[p];
+        if (e >= 0 && e < experts && slot_of_pair[p] >= 0) slot_of_pair[p] += start_row[e];
+    }
+}
+
+// xg[slot_of_pair[p], :] = bfloat16(weight * h[p / top, :]); a block per pair, 16 bytes per thread and turn
+__global__ void __launch_bounds__(128)
+moe_tile_gather_kernel(const __nv_bfloat16* __restrict__ h, const int* __restrict__ slot_of_pair, const float* __restrict__ wts,
+                       int width, int top, int weight_input, __nv_bfloat16* __restrict__ xg) {
+    pdl_trigger();
+    pdl_wait();
+    const int p = blockIdx.x;
+    const int slot = slot_of_pair[p];
+    if (slot < 0) return;
+    const float wt = weight_input ? wts[p] : 1.0f;
+    const uint4* src = reinterpret_cast<const uint4*>(h + (size_t)(p / top) * width);
+    uint4* dst = reinterpret_cast<uint4*>(xg + (size_t)slot * width);
+    for (int i = threadIdx.x; i < width / 8; i += blockDim.x) {
+        uint4 raw = src[i];
+        if (weight_input) {
+            __nv_bfloat162* v = reinterpret_cast<__nv_bfloat162*>(&raw);
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const float2 f = __bfloat1622float2(v[u]);
+                v[u] = __floats2bfloat162_rn(wt * f.x, wt * f.y);
+            }
+        }
+        dst[i] = raw;
+    }
+}
+
+// out[r, :] = sum over the row's choices, in order, of out_g[slot_of_pair[r * top + k], :]  (times the weight when it
+// multiplies the output); width a multiple of 4
+__global__ void __launch_bounds__(256)
+moe_tile_sum_kernel(const float* __restrict__ out_g, const int* __restrict__ slot_of_pair, const float* __restrict__ wts,
+                    int width, int top, int weight_input, float* __restrict__ out) {
+    pdl_trigger();
+    pdl_wait();
+    const int r = blockIdx.x;
+    for (int c = threadIdx.x * 4; c < width; c += blockDim.x * 4) {
+        float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int k = 0; k < top; ++k) {
+            const int slot = slot_of_pair[r * top + k];
+            if (slot < 0) continue;
+            const float wt = weight_input ? 1.0f : wts[r * top + k];
+            const float4 v = *reinterpret_cast<const float4*>(out_g + (size_t)slot * width + c);
+            a.x += wt * v.x; a.y += wt * v.y; a.z += wt * v.z; a.w += wt * v.w;
+        }
+        *reinterpret_cast<float4*>(out + (size_t)r * width + c) = a;
+    }
+}
+
 }  // namespace imparo
 
 using namespace imparo;
@@ -360,8 +473,9 @@ extern "C" int imparo_moe_route(const void* h, int dtype, const float* w_r, int 
                                 int softmax_scores, int renormalise, int* ids, float* wts, cudaStream_t stream) {
     if (n_rows <= 0) return 0;
     if (top < 1 || top > experts || top > 32 || experts > 2048) return -2;
-    const size_t smem = (size_t)4 * experts * sizeof(float);
-    dim3 grid((n_rows + 3) / 4);
+    const size_t smem = (size_t)(width + experts) * sizeof(float);
+    if (smem > 48 * 1024) return -25;
+    dim3 grid(n_rows);
     if (dtype == IMPARO_DT_F32)
         launch(moe_route_kernel<float>, grid, dim3(128), smem, stream, (const float*)h, w_r, n_rows, width, experts, top,
                softmax_scores, renormalise, ids, wts);
@@ -430,6 +544,38 @@ extern "C" int imparo_moe_grouped(const void* h, const void* w_gu, const void* w
     const size_t total = (size_t)n_rows * width;
     launch(moe_sum_pairs_kernel, dim3((unsigned)((total + 255) / 256 > 4096 ? 4096 : (total + 255) / 256)), dim3(256), 0, stream,
            (const float*)pair_out, n_rows, width, top, out);
+    IMPARO_CHECK_LAUNCH();
+    return 0;
+}
+
+extern "C" int imparo_gemm_prefill_grouped(const void* x, int ldx, const void* w, int n_groups, void* out, int ldo, int m_tiles,
+                                           int N, int K, int epilogue, const int* tile_group, int* status, cudaStream_t stream);
+
+// bfloat16, width and ff multiples of 8, at most 256 experts: rows sorted into tiles of 128 per expert and both products on
+// the tensor-memory kernel (SwiGLU in the first one's epilogue).  m_tiles = n_pairs / 128 + experts; xg bfloat16
+// [m_tiles * 128, width]; mid_g bfloat16 [m_tiles * 128, ff]; out_g float32 [m_tiles * 128, width]; scratch_i int32
+// [n_pairs + m_tiles]; out float32 [n_rows, width].  Five launches.  -25: not a case for this path.
+extern "C" int imparo_moe_tiles(const void* h, const void* w_gu, const void* w_down, const int* ids, const float* wts, int n_rows,
+                                int width, int ff, int top, int experts, int weight_input, void* xg, void* mid_g, float* out_g,
+                                int* scratch_i, float* out, int* status, cudaStream_t stream) {
+    if (n_rows <= 0) return 0;
+    if (width % 8 != 0 || ff % 8 != 0 || experts > 256) return -25;
+    const int n_pairs = n_rows * top;
+    const int m_tiles = n_pairs / TILE_ROWS + experts;
+    int* slot_of_pair = scratch_i;
+    int* tile_group = scratch_i + n_pairs;
+    launch(moe_tile_plan_kernel, dim3(1), dim3(1024), (size_t)34 * experts * sizeof(int), stream, ids, n_pairs, experts, slot_of_pair,
+           tile_group, m_tiles);
+    IMPARO_CHECK_LAUNCH();
+    launch(moe_tile_gather_kernel, dim3(n_pairs), dim3(128), 0, stream, (const __nv_bfloat16*)h, (const int*)slot_of_pair, wts, width,
+           top, weight_input, (__nv_bfloat16*)xg);
+    IMPARO_CHECK_LAUNCH();
+    int rc = imparo_gemm_prefill_grouped(xg, width, w_gu, experts, mid_g, ff, m_tiles, ff, width, 3, tile_group, status, stream);
+    if (rc) return rc;
+    rc = imparo_gemm_prefill_grouped(mid_g, ff, w_down, experts, out_g, width, m_tiles, width, ff, 1, tile_group, status, stream);
+    if (rc) return rc;
+    launch(moe_tile_sum_kernel, dim3(n_rows), dim3(256), 0, stream, (const float*)out_g, (const int*)slot_of_pair, wts, width, top,
+           weight_input, out);
     IMPARO_CHECK_LAUNCH();
     return 0;
 }

@@ -88,13 +88,13 @@ def _declare_kernels(lib):
              [P, P, P, I, P, P, P, I, I, I, I, c_float, P, P, P, I, I, I, I, I, I, P, S])
     _declare(lib, "imparo_attention_split_combine", [P, P, P, I, I, I, I, I, S])
     _declare(lib, "imparo_attention_decode_mma",
-             [P, P, P, P, P, P, I, I, I, I, c_float, P, P, P, I, I, I, I, I, I, I, I, P, S])
+             [P, P, P, P, P, P, I, I, I, I, c_float, P, P, P, I, I, I, I, I, I, I, I, c_float, P, S])
     _declare(lib, "imparo_attention_decode_mma_qkv",
              [P, I, c_int64, P, P, P, I, c_float, P, P, P, P, P, I, I, I, I, c_float, P, P, P, I, I, I, I, I, I, P, S])
     _declare(lib, "imparo_attention_prefill",
              [P, P, P, P, P, I, P, I, I, I, I, c_float, P, I, I, I, I, P, S])
     _declare(lib, "imparo_attention_prefill_tc",
-             [P, P, P, P, P, I, P, I, I, I, I, c_float, P, I, I, I, I, I, P, S])
+             [P, P, P, P, P, I, P, I, I, I, I, c_float, c_float, P, I, I, I, I, I, P, S])
     _declare(lib, "imparo_gated_conv", [P, I, P, P, P, P, P, P, P, I, I, I, I, I, c_int64, P, S])
     _declare(lib, "imparo_fold_partials", [P, I, c_int64, P, I, c_int64, S])
     _declare(lib, "imparo_gather_rows_f32", [P, P, P, I, I, S])
@@ -125,6 +125,7 @@ def _declare_kernels(lib):
     _declare(lib, "imparo_gate_group_rmsnorm", [P, P, I, c_int64, P, c_float, P, I, I, I, I, S])
     _declare(lib, "imparo_moe_route", [P, I, P, I, I, I, I, I, I, P, P, S])
     _declare(lib, "imparo_moe_rows", [P, P, P, I, P, P, I, I, I, I, I, I, P, P, S])
+    _declare(lib, "imparo_moe_tiles", [P, P, P, P, P, I, I, I, I, I, I, P, P, P, P, P, P, S])
     _declare(lib, "imparo_moe_grouped", [P, P, P, I, P, P, I, I, I, I, I, I, P, P, P, P, S])
     _declare(lib, "imparo_linear_attention_recurrent", [P, P, P, c_int64, I, I, P, P, P, P, I, I, P, I, I, I, P, S])
     _declare(lib, "imparo_linear_attention_chunked", [P, P, P, c_int64, I, I, P, P, P, I, I, P, P, I, I, P, I, I, I, P, S])

@@ -735,9 +735,10 @@ def split_plan(n_tok: int, nkv: int, upper_context: int, sms: Optional[int] = No
 
 def paged_attention_split(q, k_cache, v_cache, positions, item_of_token, table, page_size, n_pages, window, scale,
                           out, part_acc, part_ml, chunk, n_splits, nh, nkv, hd, status, mma: bool = True,
-                          fresh: int = 0, overlap_prev: bool = False, sink: bool = False) -> bool:
+                          fresh: int = 0, overlap_prev: bool = False, sink: bool = False, softcap: float = 0.0) -> bool:
     """Split-key attention (one CTA per key chunk, kv head and query token, then an ordered
-    combine).  Returns False, having launched nothing, when the group size is above 8.
+    combine).  Returns False, having launched nothing, when the group size is above 8, or when a soft cap on the scores
+    (softcap c > 0: c * tanh(score / c)) is asked of the kernel without tensor cores, which has none.
 
     out None: the partial results stay in part_acc / part_ml, uncombined, for a consumer that combines them itself
     (linear_of_attention_partials).
@@ -755,11 +756,13 @@ def paged_attention_split(q, k_cache, v_cache, positions, item_of_token, table, 
     the partials are left uncombined by the first kernel and the combine runs as a launch of its own (out is needed)."""
     if nh // nkv > 8:
         return False
+    if softcap and not (mma and q.dtype == torch.bfloat16 and hd in (64, 128) and chunk >= 64):
+        return False
     if sink:
         _need(out is not None, "paged_attention_split: a sink is added by the combine, which needs out")
         ok = paged_attention_split(q, k_cache, v_cache, positions, item_of_token, table, page_size, n_pages, window, scale,
                                    None, part_acc, part_ml, chunk, n_splits, nh, nkv, hd, status, mma=mma, fresh=fresh,
-                                   overlap_prev=overlap_prev)
+                                   overlap_prev=overlap_prev, softcap=softcap)
         if ok:
             attention_split_combine(part_acc, part_ml, out, q.shape[0] * nh, hd, n_splits, sink=True)
         return ok
@@ -782,7 +785,8 @@ def paged_attention_split(q, k_cache, v_cache, positions, item_of_token, table, 
         rc = _lib.kernels().imparo_attention_decode_mma(
             _ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(positions), _ptr(item_of_token), _ptr(table),
             table.shape[1], page_size, n_pages, int(window or 0), float(scale), _ptr(out), _ptr(part_acc), _ptr(part_ml),
-            T, nh, nkv, hd, int(chunk), int(n_splits), int(fresh), int(bool(overlap_prev)), _ptr(status), _stream())
+            T, nh, nkv, hd, int(chunk), int(n_splits), int(fresh), int(bool(overlap_prev)), float(softcap or 0.0), _ptr(status),
+            _stream())
     else:
         rc = _lib.kernels().imparo_paged_attention_split(
             _ptr(q), _ptr(k_cache), _ptr(v_cache), _code(q), _ptr(positions), _ptr(item_of_token), _ptr(table),
@@ -835,7 +839,7 @@ def attention_decode_from_qkv(qkv, positions, item_of_token, q_w, k_w, inv_freq,
 
 def attention_prefill(q, k_cache, v_cache, item_row_start, item_start_pos, n_items, table, page_size, n_pages, window,
                       scale, out, nh, nkv, hd, status, kernel: str = "auto", dependents_after_wait: bool = False,
-                      sink: bool = False):
+                      sink: bool = False, softcap: float = 0.0):
     """Tensor-core attention for prompt portions (bfloat16, head size 64 or 128, at most 8
     query heads per kv head).  Returns False, having launched nothing, for other shapes.
 
@@ -848,10 +852,12 @@ def attention_prefill(q, k_cache, v_cache, item_row_start, item_start_pos, n_ite
     (IMPARO_ATTN_PREFILL=mma in the environment makes "auto" skip it).
 
     sink: the softmax's denominator counts one more term of score 0 that has no value (the tcgen05 kernels only;
-    where they decline the result is False)."""
+    where they decline the result is False).  softcap c > 0: the scaled score becomes c * tanh(score / c) (the tcgen05
+    kernels only, likewise)."""
     if q.dtype != torch.bfloat16 or hd not in (64, 128) or nh // nkv > 8:
         return False
-    if sink and kernel == "auto" and _S.switches.attn_prefill == "mma":
+    only_tc = bool(sink) or bool(softcap)      # variants that only the tcgen05 kernels have
+    if only_tc and kernel == "auto" and _S.switches.attn_prefill == "mma":
         return False
     _cuda(q, k_cache, v_cache, item_row_start, item_start_pos, table, out, status)
     T = q.shape[0]
@@ -862,9 +868,10 @@ def attention_prefill(q, k_cache, v_cache, item_row_start, item_start_pos, n_ite
     _need(table.dtype == torch.int32 and table.dim() == 2 and table.shape[0] >= n_items, "block table must be int32 [items, blocks]")
     _need(item_row_start.numel() >= n_items + 1 and item_start_pos.numel() >= n_items, "attention_prefill: item arrays")
     _need(kernel in ("auto", "tcgen05", "tcgen05_one_tile", "mma"), "attention_prefill: kernel is auto, tcgen05, tcgen05_one_tile or mma")
-    args = (_ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(item_row_start), _ptr(item_start_pos), n_items, _ptr(table),
-            table.shape[1], page_size, n_pages, int(window or 0), float(scale), _ptr(out), T, nh, nkv, hd, _ptr(status),
-            _stream())
+    head = (_ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(item_row_start), _ptr(item_start_pos), n_items, _ptr(table),
+            table.shape[1], page_size, n_pages, int(window or 0), float(scale))
+    tail = (_ptr(out), T, nh, nkv, hd, _ptr(status), _stream())
+    args = head + tail
     if kernel == "auto":
         kernel = _S.switches.attn_prefill
     if kernel in ("auto", "tcgen05", "tcgen05_one_tile"):
@@ -873,14 +880,14 @@ def attention_prefill(q, k_cache, v_cache, item_row_start, item_start_pos, n_ite
         # part of the step's shape
         two_tiles = kernel == "tcgen05" or (kernel == "auto" and table.shape[1] * page_size >= 1024)
         late = bool(dependents_after_wait)      # without programmatic launches the two kernels simply run in stream order
-        rc = _lib.kernels().imparo_attention_prefill_tc(*args[:-2], (1 if two_tiles else 0) | (2 if late else 0) | (4 if sink else 0),
-                                                        *args[-2:])
+        rc = _lib.kernels().imparo_attention_prefill_tc(*head, float(softcap or 0.0), *tail[:-2],
+                                                        (1 if two_tiles else 0) | (2 if late else 0) | (4 if sink else 0), *tail[-2:])
         if rc != -8:
             _check(rc, "attention_prefill_tc")
             return 2 if late else True
-        if kernel != "auto" or sink:
+        if kernel != "auto" or only_tc:
             return False
-    if sink:
+    if only_tc:
         return False
     _check(_lib.kernels().imparo_attention_prefill(*args), "attention_prefill")
     return True
@@ -1292,6 +1299,38 @@ def moe_route(h: torch.Tensor, w_router: torch.Tensor, top: int, ids: torch.Tens
 
 
 MOE_GROUP_FROM = 32          # steps with at least this many (row, choice) pairs per expert on average run grouped by expert
+
+
+def moe_tiles_usable(h: torch.Tensor, w_gu: torch.Tensor) -> bool:
+    """Whether moe_experts_tiles takes these sizes: bfloat16, width and features in multiples of 8, at most 256 experts."""
+    return (h.dtype == torch.bfloat16 and h.shape[1] % 8 == 0 and (w_gu.shape[1] // 2) % 8 == 0 and w_gu.shape[0] <= 256
+            and gemm_backend() == "tcgen05")
+
+
+def moe_experts_tiles(h: torch.Tensor, w_gu: torch.Tensor, w_down: torch.Tensor, ids: torch.Tensor, wts: torch.Tensor, top: int,
+                      weight_input: bool, xg: torch.Tensor, mid_g: torch.Tensor, out_g: torch.Tensor, scratch_i: torch.Tensor,
+                      out: torch.Tensor, status: torch.Tensor) -> None:
+    """The same result as moe_experts for steps of many rows in bfloat16: the (row, choice) pairs are sorted by expert into
+    a buffer in which every expert's rows start at a multiple of 128 (xg, inputs already weighted), and both products run
+    on the persistent tensor-memory kernel in its grouped form (silu(gate) * up in the first one's epilogue).  With
+    m_tiles = rows * top // 128 + experts: xg bfloat16 [m_tiles * 128, width], mid_g bfloat16 [m_tiles * 128, ff], out_g
+    float32 [m_tiles * 128, width], scratch_i int32 [rows * top + m_tiles]."""
+    _cuda(h, w_gu, w_down, ids, wts, xg, mid_g, out_g, scratch_i, out, status)
+    n, width = h.shape
+    E, ff2, _ = w_gu.shape
+    ff = ff2 // 2
+    m_tiles = n * top // 128 + E
+    _need(moe_tiles_usable(h, w_gu), "moe_experts_tiles: bfloat16, width and features multiples of 8, at most 256 experts")
+    _need(w_gu.dtype == h.dtype and w_down.dtype == h.dtype and xg.dtype == h.dtype and mid_g.dtype == h.dtype,
+          "moe_experts_tiles: one dtype for h, the experts and the sorted buffers")
+    _need(xg.numel() >= m_tiles * 128 * width and mid_g.numel() >= m_tiles * 128 * ff and out_g.dtype == torch.float32
+          and out_g.numel() >= m_tiles * 128 * width and scratch_i.dtype == torch.int32 and scratch_i.numel() >= n * top + m_tiles,
+          "moe_experts_tiles: scratch too small")
+    _need(out.dtype == torch.float32 and tuple(out.shape) == (n, width), "moe_experts_tiles: out float32 [rows, width]")
+    _check(_lib.kernels().imparo_moe_tiles(_ptr(h), _ptr(w_gu), _ptr(w_down), _ptr(ids), _ptr(wts), n, width, ff, int(top), E,
+                                           int(bool(weight_input)), _ptr(xg), _ptr(mid_g), _ptr(out_g), _ptr(scratch_i), _ptr(out),
+                                           _ptr(status), _stream()), "moe_tiles")
+    COUNTS["own"] += 4
 
 
 def moe_experts(h: torch.Tensor, w_gu: torch.Tensor, w_down: torch.Tensor, ids: torch.Tensor, wts: torch.Tensor, top: int,

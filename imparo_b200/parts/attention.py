@@ -187,7 +187,7 @@ class AttentionMixer(Part):
                                  self.position.magnitude, q, kv.k, kv.v, table, kv.page_size, kv.n_pages, nh, nkv, hd, vd, rt.status)
         out = rt.workspace.get("attn_out", (T, nh * vd), rt.act_dtype, first="tokens")
         done = False
-        if self.softcap == 0.0 and rt.act_dtype == torch.bfloat16 and hd == vd and hd in (64, 128) and nh // self.nkv <= 8 and T <= 65535:
+        if rt.act_dtype == torch.bfloat16 and hd == vd and hd in (64, 128) and nh // self.nkv <= 8 and T <= 65535:
             # the tensor-core kernels take these sizes (the sink as a flag): prompt portions on the tcgen05 kernel, rows
             # of one token (and portions too short for a tile, or pages it does not take) on the split-key kernel
             n1 = getattr(batch, "n_single", 0)
@@ -195,12 +195,12 @@ class AttentionMixer(Part):
             if batch.max_tokens_per_item >= 8 and 0 < n1 < batch.n_items:
                 done = ops.attention_prefill(q, kv.k, kv.v, batch.item_row_start[n1:], batch.item_start_pos[n1:],
                                              batch.n_items - n1, table[n1:], kv.page_size, kv.n_pages, self.window, self.scale,
-                                             out, nh, self.nkv, hd, rt.status, sink=self.sink)
+                                             out, nh, self.nkv, hd, rt.status, sink=self.sink, softcap=self.softcap)
                 first_split = n1 if done else T
             elif batch.max_tokens_per_item >= 8:
                 done = ops.attention_prefill(q, kv.k, kv.v, batch.item_row_start, batch.item_start_pos, batch.n_items, table,
                                              kv.page_size, kv.n_pages, self.window, self.scale, out, nh, self.nkv, hd, rt.status,
-                                             sink=self.sink)
+                                             sink=self.sink, softcap=self.softcap)
                 first_split = 0 if done else T
             else:
                 first_split = T
@@ -212,7 +212,7 @@ class AttentionMixer(Part):
                 part_ml = rt.workspace.get("attn_part_ml", (n * nh * n_splits * 2,), torch.float32, reserve=room * 2)
                 done = ops.paged_attention_split(q[:n], kv.k, kv.v, batch.positions[:n], batch.item_of_token[:n], table,
                                                  kv.page_size, kv.n_pages, self.window, self.scale, out[:n], part_acc, part_ml,
-                                                 chunk, n_splits, nh, self.nkv, hd, rt.status, sink=self.sink)
+                                                 chunk, n_splits, nh, self.nkv, hd, rt.status, sink=self.sink, softcap=self.softcap)
         if not done:
             ops.attention_any(q, kv.k, kv.v, batch.positions, batch.item_of_token, table, kv.page_size, kv.n_pages, self.window,
                               self.scale, self.sink, out, nh, self.nkv, hd, vd, rt.status, softcap=self.softcap)

@@ -22,6 +22,7 @@ class RoutedExperts(Part):
 
     forward(x, batch, residual, accumulate=False) overwrites `residual` (a float32 [rows, hidden] buffer)."""
     GROUP_FROM = 65           # steps with at least this many (row, expert) pairs run sorted by expert, in tiles
+    TILES_FROM = 256          # and from this many on (bfloat16, aligned sizes) on the tensor-memory product, tiles of 128 rows
 
     NAMES = {"router": "router", "gate": "e{e}.gate", "up": "e{e}.up", "down": "e{e}.down"}
 
@@ -68,9 +69,18 @@ class RoutedExperts(Part):
         ids = ws.get("moe_ids", (T, self.top), torch.int32, first="tokens")
         wts = ws.get("moe_wts", (T, self.top), torch.float32, first="tokens")
         ops.moe_route(x, self.w_router, self.top, ids, wts, softmax=self.score == "softmax", renormalise=self.renormalise)
+        pairs = T * self.top
+        if pairs >= self.TILES_FROM and ops.moe_tiles_usable(x, self.w_gu):
+            # many rows in bfloat16: sorted into tiles of 128 rows per expert, both products on the tensor-memory kernel
+            rows = (pairs // 128 + self.experts) * 128
+            ops.moe_experts_tiles(x, self.w_gu, self.w_down, ids, wts, self.top, self.weight_on == "input",
+                                  ws.get("moe_sorted_in", (rows, self.hidden), rt.act_dtype),
+                                  ws.get("moe_sorted_mid", (rows, self.ff), rt.act_dtype),
+                                  ws.get("moe_sorted_out", (rows, self.hidden), torch.float32),
+                                  ws.get("moe_tile_plan", (pairs + rows // 128,), torch.int32), residual, rt.status)
+            return
         mid = ws.get("moe_mid", (T * self.top, self.ff), rt.act_dtype, first="tokens")
         scratch = None
-        pairs = T * self.top
         if pairs >= self.GROUP_FROM:
             scratch = (ws.get("moe_pair_out", (pairs, self.hidden), torch.float32, first="tokens"),
                        ws.get("moe_plan", (pairs + self.experts + 2 + 3 * (pairs // 32 + self.experts),), torch.int32))

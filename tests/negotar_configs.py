@@ -40,19 +40,20 @@ NEG_A = {
 }
 
 # the state-space mixer first, groups == heads, one norm stretch, two taps; attention without shared values or cap,
-# the whole head rotated with plain frequencies; one expert per token; a layer without feed-forward; no logit scale
+# the whole head rotated with plain frequencies; a layer without feed-forward; no logit scale
 NEG_B = {
     "architecture": "Negotar", "vocab": 300, "width": 96, "norm": {"eps": 1e-6},
     "layers": [
-        _with(_ssm(3, 32, 8, 3, 2, 1), 5, 1, 64),
-        _with(_attn(3, 3, 32, 32, 0.2, rot={"dims": 32, "base": 500.0}), 5, 1, 64),
+        _with(_ssm(3, 32, 8, 3, 2, 1), 5, 2, 64),
+        _with(_attn(3, 3, 32, 32, 0.2, rot={"dims": 32, "base": 500.0}), 5, 2, 64),
         _with(_ssm(3, 32, 8, 3, 2, 1)),
         _with(_attn(6, 1, 16, 48, 0.25, rot={"dims": 2, "base": 7.0}, softcap=50.0), 4, 3, 24),
     ],
 }
 
 # a width that is no multiple of 8; sizes that are no multiples of 16 or 32; no rotation; every expert used by every
-# token; shared values on the second and fourth layer only (the first attention layer has none); five taps, one group
+# token; shared values on the second and fourth layer only (the first attention layer has none); five taps, one group; one expert
+# per token in the last layer
 NEG_C = {
     "architecture": "Negotar", "vocab": 257, "width": 100, "norm": {"eps": 3e-6}, "logit_scale": 0.5,
     "layers": [

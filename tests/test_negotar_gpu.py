@@ -422,7 +422,7 @@ def test_state_space_kernels(dtype, heads, vdim, N, groups, taps, norm_groups):
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("width,ff,experts,top,rows", [(64, 40, 6, 2, 5), (96, 64, 5, 1, 90), (100, 30, 3, 3, 33), (128, 64, 8, 2, 300),
-                                                       (72, 50, 7, 2, 1)])
+                                                       (72, 50, 7, 2, 1), (256, 200, 5, 3, 700), (64, 328, 40, 4, 130)])
 def test_routed_expert_kernels(dtype, width, ff, experts, top, rows):
     """Router, choice and the experts, pair by pair and sorted into tiles, against the plain routed feed-forward."""
     import torch
@@ -460,6 +460,16 @@ def test_routed_expert_kernels(dtype, width, ff, experts, top, rows):
         ops.moe_experts(hd, w_gu, w_down, ids, wts, top, True, mid, out, scratch=scratch)
         got = out.cpu().numpy()
         assert np.abs(got - want)[sure].max() <= (3e-5 if dtype == "float32" else 2e-2) * np.abs(want).max(), grouped
+    if ops.moe_tiles_usable(hd, w_gu):
+        # sorted into tiles of 128 rows per expert, both products on the tensor-memory kernel
+        m_rows = (pairs // 128 + experts) * 128
+        status = ops.new_status("cuda")
+        out = torch.full((rows, width), 9.0, device="cuda")
+        ops.moe_experts_tiles(hd, w_gu, w_down, ids, wts, top, True, torch.empty(m_rows, width, dtype=tdt, device="cuda"),
+                              torch.empty(m_rows, ff, dtype=tdt, device="cuda"), torch.empty(m_rows, width, device="cuda"),
+                              torch.empty(pairs + m_rows // 128, dtype=torch.int32, device="cuda"), out, status)
+        ops.read_status(status)
+        assert np.abs(out.cpu().numpy() - want)[sure].max() <= 2e-2 * np.abs(want).max()
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
