@@ -81,6 +81,36 @@ mamba2_conv_state_kernel(const T* __restrict__ proj, size_t stride, int x_off, i
 }
 
 // ---- (2) the recurrence, row by row ------------------------------------------------------------------------------
+// One row of the recurrence for this thread's state column: S = decay S + dx B;  returns C . S.  B and C come from shared
+// memory four at a time; entries from N on are zero there and in S, so the loops run over the whole NMAX.  Four partial
+// sums keep the additions from waiting on one another; their order is fixed.
+template <int NMAX>
+__device__ __forceinline__ float state_step(float (&S)[NMAX], const float* __restrict__ b, const float* __restrict__ c, float decay, float dx) {
+    float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
+#pragma unroll
+    for (int n = 0; n < NMAX; n += 4) {
+        const float4 b4 = *reinterpret_cast<const float4*>(b + n);
+        const float4 c4 = *reinterpret_cast<const float4*>(c + n);
+        S[n] = fmaf(decay, S[n], b4.x * dx);         a0 = fmaf(S[n], c4.x, a0);
+        S[n + 1] = fmaf(decay, S[n + 1], b4.y * dx); a1 = fmaf(S[n + 1], c4.y, a1);
+        S[n + 2] = fmaf(decay, S[n + 2], b4.z * dx); a2 = fmaf(S[n + 2], c4.z, a2);
+        S[n + 3] = fmaf(decay, S[n + 3], b4.w * dx); a3 = fmaf(S[n + 3], c4.w, a3);
+    }
+    return (a0 + a1) + (a2 + a3);
+}
+
+template <int NMAX>
+__device__ __forceinline__ void state_step_no_out(float (&S)[NMAX], const float* __restrict__ b, float decay, float dx) {
+#pragma unroll
+    for (int n = 0; n < NMAX; n += 4) {
+        const float4 b4 = *reinterpret_cast<const float4*>(b + n);
+        S[n] = fmaf(decay, S[n], b4.x * dx);
+        S[n + 1] = fmaf(decay, S[n + 1], b4.y * dx);
+        S[n + 2] = fmaf(decay, S[n + 2], b4.z * dx);
+        S[n + 3] = fmaf(decay, S[n + 3], b4.w * dx);
+    }
+}
+
 // grid (heads, items, ceil(vdim / 32)), one warp each
 template <int NMAX>
 __global__ void __launch_bounds__(32)
@@ -88,7 +118,7 @@ mamba2_scan_kernel(const float* __restrict__ xbc, const float* __restrict__ dt, 
                    const float* __restrict__ D, float* __restrict__ state, const int* __restrict__ item_row_start,
                    const int* __restrict__ item_slot, int n_slots, float* __restrict__ y,
                    int heads, int vdim, int N, int groups, int* status) {
-    __shared__ float bc[2][NMAX];
+    __shared__ __align__(16) float bc[2][NMAX];
     pdl_trigger();
     const int h = blockIdx.x, item = blockIdx.y, lane = threadIdx.x;
     const int p = blockIdx.z * 32 + lane;
@@ -108,6 +138,7 @@ mamba2_scan_kernel(const float* __restrict__ xbc, const float* __restrict__ dt, 
     float S[NMAX];
 #pragma unroll
     for (int n = 0; n < NMAX; ++n) S[n] = (live && n < N) ? sp[(size_t)n * vdim] : 0.f;
+    for (int n = N + lane; n < NMAX; n += 32) { bc[0][n] = 0.f; bc[1][n] = 0.f; }
     for (int t = first; t < last; ++t) {
         const float* row = xbc + (size_t)t * channels;
         __syncwarp();
@@ -117,17 +148,8 @@ mamba2_scan_kernel(const float* __restrict__ xbc, const float* __restrict__ dt, 
         }
         __syncwarp();
         const float step = dt[(size_t)t * heads + h];
-        const float decay = expf(a * step);
         const float xv = live ? row[h * vdim + p] : 0.f;
-        const float dx = step * xv;
-        float acc = 0.f;
-#pragma unroll
-        for (int n = 0; n < NMAX; ++n) {
-            if (n < N) {
-                S[n] = decay * S[n] + bc[0][n] * dx;
-                acc += S[n] * bc[1][n];
-            }
-        }
+        const float acc = state_step<NMAX>(S, bc[0], bc[1], expf(a * step), step * xv);
         if (live) y[(size_t)t * inner + h * vdim + p] = acc + d_skip * xv;
     }
     if (live) {
@@ -165,7 +187,7 @@ mamba2_chunk_state_kernel(const float* __restrict__ xbc, const float* __restrict
                           const int* __restrict__ chunk_lo, const int* __restrict__ chunk_hi,
                           float* __restrict__ chunk_state, float* __restrict__ chunk_decay,
                           int heads, int vdim, int N, int groups) {
-    __shared__ float bs[NMAX];
+    __shared__ __align__(16) float bs[NMAX];
     pdl_trigger();
     const int h = blockIdx.x, c = blockIdx.y, lane = threadIdx.x;
     const int p = blockIdx.z * 32 + lane;
@@ -180,18 +202,15 @@ mamba2_chunk_state_kernel(const float* __restrict__ xbc, const float* __restrict
 #pragma unroll
     for (int n = 0; n < NMAX; ++n) S[n] = 0.f;
     float total = 0.f;                                            // sum of a * dt over the chunk
+    for (int n = N + lane; n < NMAX; n += 32) bs[n] = 0.f;
     for (int t = lo; t < hi; ++t) {
         const float* row = xbc + (size_t)t * channels;
         __syncwarp();
         for (int n = lane; n < N; n += 32) bs[n] = row[inner + g * N + n];
         __syncwarp();
         const float step = dt[(size_t)t * heads + h];
-        const float decay = expf(a * step);
         total += a * step;
-        const float dx = live ? step * row[h * vdim + p] : 0.f;
-#pragma unroll
-        for (int n = 0; n < NMAX; ++n)
-            if (n < N) S[n] = decay * S[n] + bs[n] * dx;
+        state_step_no_out<NMAX>(S, bs, expf(a * step), live ? step * row[h * vdim + p] : 0.f);
     }
     if (live) {
         float* out = chunk_state + (((size_t)c * heads + h) * N) * vdim + p;
@@ -220,7 +239,21 @@ mamba2_chunk_scan_kernel(float* __restrict__ chunk_state, const float* __restric
     for (int e = blockIdx.z * blockDim.x + threadIdx.x; e < per; e += gridDim.z * blockDim.x) {
         float* sp = state + ((size_t)slot * heads + h) * per + e;
         float S = *sp;
-        for (int c = c0; c < c1; ++c) {
+        int c = c0;
+        for (; c + 4 <= c1; c += 4) {                              // four chunks' loads in flight
+            float own[4], dec[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                own[u] = chunk_state[((size_t)(c + u) * heads + h) * per + e];
+                dec[u] = expf(chunk_decay[(size_t)(c + u) * heads + h]);
+            }
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                chunk_state[((size_t)(c + u) * heads + h) * per + e] = S;
+                S = dec[u] * S + own[u];
+            }
+        }
+        for (; c < c1; ++c) {
             float* cs = chunk_state + ((size_t)c * heads + h) * per + e;
             const float own = *cs;
             *cs = S;
@@ -237,7 +270,7 @@ mamba2_chunk_out_kernel(const float* __restrict__ xbc, const float* __restrict__
                         const float* __restrict__ D, const int* __restrict__ chunk_lo, const int* __restrict__ chunk_hi,
                         const float* __restrict__ chunk_state, float* __restrict__ y,
                         int heads, int vdim, int N, int groups) {
-    __shared__ float bc[2][NMAX];
+    __shared__ __align__(16) float bc[2][NMAX];
     pdl_trigger();
     const int h = blockIdx.x, c = blockIdx.y, lane = threadIdx.x;
     const int p = blockIdx.z * 32 + lane;
@@ -253,6 +286,7 @@ mamba2_chunk_out_kernel(const float* __restrict__ xbc, const float* __restrict__
     float S[NMAX];
 #pragma unroll
     for (int n = 0; n < NMAX; ++n) S[n] = (live && n < N) ? sp[(size_t)n * vdim] : 0.f;
+    for (int n = N + lane; n < NMAX; n += 32) { bc[0][n] = 0.f; bc[1][n] = 0.f; }
     for (int t = lo; t < hi; ++t) {
         const float* row = xbc + (size_t)t * channels;
         __syncwarp();
@@ -262,17 +296,8 @@ mamba2_chunk_out_kernel(const float* __restrict__ xbc, const float* __restrict__
         }
         __syncwarp();
         const float step = dt[(size_t)t * heads + h];
-        const float decay = expf(a * step);
         const float xv = live ? row[h * vdim + p] : 0.f;
-        const float dx = step * xv;
-        float acc = 0.f;
-#pragma unroll
-        for (int n = 0; n < NMAX; ++n) {
-            if (n < N) {
-                S[n] = decay * S[n] + bc[0][n] * dx;
-                acc += S[n] * bc[1][n];
-            }
-        }
+        const float acc = state_step<NMAX>(S, bc[0], bc[1], expf(a * step), step * xv);
         if (live) y[(size_t)t * inner + h * vdim + p] = acc + d_skip * xv;
     }
 }

@@ -19,12 +19,59 @@
 
 namespace imparo {
 
+// A warp's dot product of a matrix row with a vector in shared memory (32-bit).  When the row is 16 bytes wide per
+// lane and turn (VEC), lanes read 16 bytes at a time, four loads in flight; the order of additions is fixed either way.
+template <typename T> struct Vec16 { static constexpr int N = 16 / (int)sizeof(T); };
+
+template <typename T>
+__device__ __forceinline__ float dot16(const uint4 raw, const float* __restrict__ x) {
+    float a = 0.f;
+    if constexpr (sizeof(T) == 2) {
+        const __nv_bfloat162* v = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            const float2 f = __bfloat1622float2(v[u]);
+            a = fmaf(f.x, x[2 * u], a);
+            a = fmaf(f.y, x[2 * u + 1], a);
+        }
+    } else {
+        const float* v = reinterpret_cast<const float*>(&raw);
+#pragma unroll
+        for (int u = 0; u < 4; ++u) a = fmaf(v[u], x[u], a);
+    }
+    return a;
+}
+
+template <typename T>
+__device__ __forceinline__ float warp_dot(const T* __restrict__ w, const float* __restrict__ x, int n, bool vec, int lane) {
+    float acc = 0.f;
+    if (vec) {
+        constexpr int PER = Vec16<T>::N;
+        const uint4* w4 = reinterpret_cast<const uint4*>(w);
+        const int n4 = n / PER;
+        int i = lane;
+        float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
+        for (; i + 96 < n4; i += 128) {
+            const uint4 r0 = w4[i], r1 = w4[i + 32], r2 = w4[i + 64], r3 = w4[i + 96];
+            a0 += dot16<T>(r0, x + (size_t)i * PER);
+            a1 += dot16<T>(r1, x + (size_t)(i + 32) * PER);
+            a2 += dot16<T>(r2, x + (size_t)(i + 64) * PER);
+            a3 += dot16<T>(r3, x + (size_t)(i + 96) * PER);
+        }
+        for (; i < n4; i += 32) a0 += dot16<T>(w4[i], x + (size_t)i * PER);
+        acc = (a0 + a1) + (a2 + a3);
+    } else {
+        for (int i = lane; i < n; i += 32) acc += to_f32(w[i]) * x[i];
+    }
+    return warp_sum(acc);
+}
+
 // ---- (1) router -------------------------------------------------------------------------------------------------
 template <typename T>
 __global__ void __launch_bounds__(128)
 moe_route_kernel(const T* __restrict__ h, const float* __restrict__ w_r, int n_rows, int width, int experts, int top,
                  int softmax_scores, int renormalise, int* __restrict__ ids, float* __restrict__ wts) {
-    extern __shared__ float route_smem[];                // [width] the row in 32-bit, then [experts] logits
+    extern __shared__ __align__(16) float route_smem[];  // [width] the row in 32-bit, then [experts] logits
     pdl_trigger();
     pdl_wait();
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -37,14 +84,7 @@ moe_route_kernel(const T* __restrict__ h, const float* __restrict__ w_r, int n_r
     // a warp per expert in turn; the dot product always adds in the same order (four partial sums per lane, then the
     // lanes), whatever else the launch holds
     for (int e = warp; e < experts; e += 4) {
-        const float* wr = w_r + (size_t)e * width;
-        float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
-        int i = lane;
-        for (; i + 96 < width; i += 128) {
-            a0 += wr[i] * row[i]; a1 += wr[i + 32] * row[i + 32]; a2 += wr[i + 64] * row[i + 64]; a3 += wr[i + 96] * row[i + 96];
-        }
-        for (; i < width; i += 32) a0 += wr[i] * row[i];
-        const float acc = warp_sum((a0 + a1) + (a2 + a3));
+        const float acc = warp_dot<float>(w_r + (size_t)e * width, row, width, width % 4 == 0, lane);
         if (lane == 0) s[e] = acc;
     }
     __syncthreads();
@@ -91,7 +131,7 @@ template <typename T>
 __global__ void __launch_bounds__(256)
 moe_rows_up_kernel(const T* __restrict__ h, const T* __restrict__ w_gu, const int* __restrict__ ids, const float* __restrict__ wts,
                    int width, int ff, int top, int experts, int weight_input, T* __restrict__ mid) {
-    extern __shared__ float up_smem[];
+    extern __shared__ __align__(16) float up_smem[];
     pdl_trigger();
     pdl_wait();
     const int pair = blockIdx.x, r = pair / top;
@@ -103,19 +143,12 @@ moe_rows_up_kernel(const T* __restrict__ h, const T* __restrict__ w_gu, const in
     __syncthreads();
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const T* base = w_gu + (size_t)e * 2 * ff * width;
+    const bool vec = width % Vec16<T>::N == 0 && ((uintptr_t)w_gu & 15) == 0;
     for (int j = 0; j < 4; ++j) {
         const int f = blockIdx.y * 32 + warp * 4 + j;
         if (f >= ff) break;
-        const T* g = base + (size_t)f * width;
-        const T* u = base + (size_t)(ff + f) * width;
-        float ag = 0.f, au = 0.f;
-        for (int i = lane; i < width; i += 32) {
-            const float x = up_smem[i];
-            ag += to_f32(g[i]) * x;
-            au += to_f32(u[i]) * x;
-        }
-        ag = warp_sum(ag);
-        au = warp_sum(au);
+        const float ag = warp_dot<T>(base + (size_t)f * width, up_smem, width, vec, lane);
+        const float au = warp_dot<T>(base + (size_t)(ff + f) * width, up_smem, width, vec, lane);
         if (lane == 0) mid[(size_t)pair * ff + f] = from_f32<T>(silu(ag) * au);
     }
 }
@@ -126,11 +159,12 @@ __global__ void __launch_bounds__(256)
 moe_rows_down_kernel(const T* __restrict__ mid, const T* __restrict__ w_down, const int* __restrict__ ids,
                      const float* __restrict__ wts, int width, int ff, int top, int experts, int weight_input,
                      float* __restrict__ out) {
-    extern __shared__ float down_smem[];
+    extern __shared__ __align__(16) float down_smem[];
     pdl_trigger();
     pdl_wait();
     const int r = blockIdx.x;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const bool vec = ff % Vec16<T>::N == 0 && ((uintptr_t)w_down & 15) == 0;
     float acc[4] = {0.f, 0.f, 0.f, 0.f};
     for (int k = 0; k < top; ++k) {
         const int pair = r * top + k;
@@ -143,10 +177,7 @@ moe_rows_down_kernel(const T* __restrict__ mid, const T* __restrict__ w_down, co
         for (int j = 0; j < 4; ++j) {
             const int o = blockIdx.y * 32 + warp * 4 + j;
             if (o >= width) break;
-            const T* d = w_down + ((size_t)e * width + o) * ff;
-            float a = 0.f;
-            for (int i = lane; i < ff; i += 32) a += to_f32(d[i]) * down_smem[i];
-            acc[j] += wt * warp_sum(a);
+            acc[j] += wt * warp_dot<T>(w_down + ((size_t)e * width + o) * ff, down_smem, ff, vec, lane);
         }
     }
     if (lane == 0)
