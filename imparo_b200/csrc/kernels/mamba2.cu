@@ -83,33 +83,65 @@ mamba2_conv_state_kernel(const T* __restrict__ proj, size_t stride, int x_off, i
 // ---- (2) the recurrence, row by row ------------------------------------------------------------------------------
 // One row of the recurrence for this thread's state column: S = decay S + dx B;  returns C . S.  B and C come from shared
 // memory four at a time; entries from N on are zero there and in S, so the loops run over the whole NMAX.  Four partial
-// sums keep the additions from waiting on one another; their order is fixed.
+// sums (two packed pairs) keep the additions from waiting on one another; their order is fixed.
 template <int NMAX>
 __device__ __forceinline__ float state_step(float (&S)[NMAX], const float* __restrict__ b, const float* __restrict__ c, float decay, float dx) {
-    float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
+    // two 32-bit operations per instruction (fma.rn.f32x2): each half rounds as the single operation does
+    const float2 d2 = make_float2(decay, decay), x2 = make_float2(dx, dx);
+    float2 a01 = make_float2(0.f, 0.f), a23 = make_float2(0.f, 0.f);
 #pragma unroll
     for (int n = 0; n < NMAX; n += 4) {
         const float4 b4 = *reinterpret_cast<const float4*>(b + n);
         const float4 c4 = *reinterpret_cast<const float4*>(c + n);
-        S[n] = fmaf(decay, S[n], b4.x * dx);         a0 = fmaf(S[n], c4.x, a0);
-        S[n + 1] = fmaf(decay, S[n + 1], b4.y * dx); a1 = fmaf(S[n + 1], c4.y, a1);
-        S[n + 2] = fmaf(decay, S[n + 2], b4.z * dx); a2 = fmaf(S[n + 2], c4.z, a2);
-        S[n + 3] = fmaf(decay, S[n + 3], b4.w * dx); a3 = fmaf(S[n + 3], c4.w, a3);
+        float2 s01 = make_float2(S[n], S[n + 1]), s23 = make_float2(S[n + 2], S[n + 3]);
+        s01 = __ffma2_rn(d2, s01, __fmul2_rn(make_float2(b4.x, b4.y), x2));
+        s23 = __ffma2_rn(d2, s23, __fmul2_rn(make_float2(b4.z, b4.w), x2));
+        a01 = __ffma2_rn(s01, make_float2(c4.x, c4.y), a01);
+        a23 = __ffma2_rn(s23, make_float2(c4.z, c4.w), a23);
+        S[n] = s01.x; S[n + 1] = s01.y; S[n + 2] = s23.x; S[n + 3] = s23.y;
     }
-    return (a0 + a1) + (a2 + a3);
+    return (a01.x + a01.y) + (a23.x + a23.y);
 }
 
 template <int NMAX>
 __device__ __forceinline__ void state_step_no_out(float (&S)[NMAX], const float* __restrict__ b, float decay, float dx) {
+    const float2 d2 = make_float2(decay, decay), x2 = make_float2(dx, dx);
 #pragma unroll
     for (int n = 0; n < NMAX; n += 4) {
         const float4 b4 = *reinterpret_cast<const float4*>(b + n);
-        S[n] = fmaf(decay, S[n], b4.x * dx);
-        S[n + 1] = fmaf(decay, S[n + 1], b4.y * dx);
-        S[n + 2] = fmaf(decay, S[n + 2], b4.z * dx);
-        S[n + 3] = fmaf(decay, S[n + 3], b4.w * dx);
+        float2 s01 = make_float2(S[n], S[n + 1]), s23 = make_float2(S[n + 2], S[n + 3]);
+        s01 = __ffma2_rn(d2, s01, __fmul2_rn(make_float2(b4.x, b4.y), x2));
+        s23 = __ffma2_rn(d2, s23, __fmul2_rn(make_float2(b4.z, b4.w), x2));
+        S[n] = s01.x; S[n + 1] = s01.y; S[n + 2] = s23.x; S[n + 3] = s23.y;
     }
 }
+
+// A row's B and C entries of this lane (n = lane, lane + 32, ...), its step size and its x value, fetched one row ahead
+// of the row being computed, so that their latency hides behind the arithmetic.
+template <int NMAX>
+struct RowAhead {
+    static constexpr int PER = (NMAX + 31) / 32;
+    float b[PER], c[PER], step, x;
+    __device__ __forceinline__ void fetch(const float* __restrict__ xbc, const float* __restrict__ dt, int t, int channels, int inner,
+                                          int b_off, int c_off, int x_col, int heads, int h, int N, int lane, bool live, bool want_c) {
+        const float* row = xbc + (size_t)t * channels;
+#pragma unroll
+        for (int i = 0; i < PER; ++i) {
+            const int n = lane + 32 * i;
+            b[i] = n < N ? row[b_off + n] : 0.f;
+            c[i] = (want_c && n < N) ? row[c_off + n] : 0.f;
+        }
+        step = dt[(size_t)t * heads + h];
+        x = live ? row[x_col] : 0.f;
+    }
+    __device__ __forceinline__ void put(float* __restrict__ bs, float* __restrict__ cs, int lane) const {
+#pragma unroll
+        for (int i = 0; i < PER; ++i) {
+            const int n = lane + 32 * i;
+            if (n < NMAX) { bs[n] = b[i]; if (cs) cs[n] = c[i]; }
+        }
+    }
+};
 
 // grid (heads, items, ceil(vdim / 32)), one warp each
 template <int NMAX>
@@ -138,17 +170,15 @@ mamba2_scan_kernel(const float* __restrict__ xbc, const float* __restrict__ dt, 
     float S[NMAX];
 #pragma unroll
     for (int n = 0; n < NMAX; ++n) S[n] = (live && n < N) ? sp[(size_t)n * vdim] : 0.f;
-    for (int n = N + lane; n < NMAX; n += 32) { bc[0][n] = 0.f; bc[1][n] = 0.f; }
+    RowAhead<NMAX> next;
+    const int b_off = inner + g * N, c_off = inner + groups * N + g * N, x_col = h * vdim + p;
+    if (first < last) next.fetch(xbc, dt, first, channels, inner, b_off, c_off, x_col, heads, h, N, lane, live, true);
     for (int t = first; t < last; ++t) {
-        const float* row = xbc + (size_t)t * channels;
         __syncwarp();
-        for (int n = lane; n < N; n += 32) {
-            bc[0][n] = row[inner + g * N + n];
-            bc[1][n] = row[inner + groups * N + g * N + n];
-        }
+        next.put(bc[0], bc[1], lane);
         __syncwarp();
-        const float step = dt[(size_t)t * heads + h];
-        const float xv = live ? row[h * vdim + p] : 0.f;
+        const float step = next.step, xv = next.x;
+        if (t + 1 < last) next.fetch(xbc, dt, t + 1, channels, inner, b_off, c_off, x_col, heads, h, N, lane, live, true);
         const float acc = state_step<NMAX>(S, bc[0], bc[1], expf(a * step), step * xv);
         if (live) y[(size_t)t * inner + h * vdim + p] = acc + d_skip * xv;
     }
@@ -202,15 +232,17 @@ mamba2_chunk_state_kernel(const float* __restrict__ xbc, const float* __restrict
 #pragma unroll
     for (int n = 0; n < NMAX; ++n) S[n] = 0.f;
     float total = 0.f;                                            // sum of a * dt over the chunk
-    for (int n = N + lane; n < NMAX; n += 32) bs[n] = 0.f;
+    RowAhead<NMAX> next;
+    const int b_off = inner + g * N, x_col = h * vdim + p;
+    next.fetch(xbc, dt, lo, channels, inner, b_off, 0, x_col, heads, h, N, lane, live, false);
     for (int t = lo; t < hi; ++t) {
-        const float* row = xbc + (size_t)t * channels;
         __syncwarp();
-        for (int n = lane; n < N; n += 32) bs[n] = row[inner + g * N + n];
+        next.put(bs, nullptr, lane);
         __syncwarp();
-        const float step = dt[(size_t)t * heads + h];
+        const float step = next.step, xv = next.x;
+        if (t + 1 < hi) next.fetch(xbc, dt, t + 1, channels, inner, b_off, 0, x_col, heads, h, N, lane, live, false);
         total += a * step;
-        state_step_no_out<NMAX>(S, bs, expf(a * step), live ? step * row[h * vdim + p] : 0.f);
+        state_step_no_out<NMAX>(S, bs, expf(a * step), step * xv);
     }
     if (live) {
         float* out = chunk_state + (((size_t)c * heads + h) * N) * vdim + p;
@@ -286,17 +318,15 @@ mamba2_chunk_out_kernel(const float* __restrict__ xbc, const float* __restrict__
     float S[NMAX];
 #pragma unroll
     for (int n = 0; n < NMAX; ++n) S[n] = (live && n < N) ? sp[(size_t)n * vdim] : 0.f;
-    for (int n = N + lane; n < NMAX; n += 32) { bc[0][n] = 0.f; bc[1][n] = 0.f; }
+    RowAhead<NMAX> next;
+    const int b_off = inner + g * N, c_off = inner + groups * N + g * N, x_col = h * vdim + p;
+    next.fetch(xbc, dt, lo, channels, inner, b_off, c_off, x_col, heads, h, N, lane, live, true);
     for (int t = lo; t < hi; ++t) {
-        const float* row = xbc + (size_t)t * channels;
         __syncwarp();
-        for (int n = lane; n < N; n += 32) {
-            bc[0][n] = row[inner + g * N + n];
-            bc[1][n] = row[inner + groups * N + g * N + n];
-        }
+        next.put(bc[0], bc[1], lane);
         __syncwarp();
-        const float step = dt[(size_t)t * heads + h];
-        const float xv = live ? row[h * vdim + p] : 0.f;
+        const float step = next.step, xv = next.x;
+        if (t + 1 < hi) next.fetch(xbc, dt, t + 1, channels, inner, b_off, c_off, x_col, heads, h, N, lane, live, true);
         const float acc = state_step<NMAX>(S, bc[0], bc[1], expf(a * step), step * xv);
         if (live) y[(size_t)t * inner + h * vdim + p] = acc + d_skip * xv;
     }

@@ -67,29 +67,68 @@ __device__ __forceinline__ float warp_dot(const T* __restrict__ w, const float* 
 }
 
 // ---- (1) router -------------------------------------------------------------------------------------------------
+// A block takes up to four rows, so that a router row read once serves them all; a warp per expert in turn; warp r then
+// picks for row r.  A dot product always adds in the same order, whatever else the launch holds.
 template <typename T>
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(256)
 moe_route_kernel(const T* __restrict__ h, const float* __restrict__ w_r, int n_rows, int width, int experts, int top,
-                 int softmax_scores, int renormalise, int* __restrict__ ids, float* __restrict__ wts) {
-    extern __shared__ __align__(16) float route_smem[];  // [width] the row in 32-bit, then [experts] logits
+                 int softmax_scores, int renormalise, int rows_per_block, int* __restrict__ ids, float* __restrict__ wts) {
+    extern __shared__ __align__(16) float route_smem[];  // [rows][width] the rows in 32-bit, then [rows][experts] logits
     pdl_trigger();
     pdl_wait();
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const int r = blockIdx.x;
-    float* row = route_smem;
-    float* s = route_smem + width;
-    const T* hr = h + (size_t)r * width;
-    for (int i = threadIdx.x; i < width; i += blockDim.x) row[i] = to_f32(hr[i]);
+    const int r0 = blockIdx.x * rows_per_block;
+    const int R = min(rows_per_block, n_rows - r0);
+    float* rows = route_smem;
+    float* logits = route_smem + (size_t)rows_per_block * width;
+    for (int i = threadIdx.x; i < R * width; i += blockDim.x) rows[i] = to_f32(h[(size_t)r0 * width + i]);
     __syncthreads();
-    // a warp per expert in turn; the dot product always adds in the same order (four partial sums per lane, then the
-    // lanes), whatever else the launch holds
-    for (int e = warp; e < experts; e += 4) {
-        const float acc = warp_dot<float>(w_r + (size_t)e * width, row, width, width % 4 == 0, lane);
-        if (lane == 0) s[e] = acc;
+    const bool vec = width % 4 == 0;
+    for (int e = warp; e < experts; e += 8) {
+        const float* wr = w_r + (size_t)e * width;
+        float acc[4] = {0.f, 0.f, 0.f, 0.f};
+        if (vec) {
+            const float4* w4 = reinterpret_cast<const float4*>(wr);
+            const int n4 = width / 4;
+            int i = lane;
+            for (; i + 32 < n4; i += 64) {                   // two loads in flight
+                const float4 u = w4[i], v = w4[i + 32];
+#pragma unroll
+                for (int r = 0; r < 4; ++r) {
+                    if (r < R) {
+                        const float* x = rows + (size_t)r * width;
+                        acc[r] += u.x * x[4 * i] + u.y * x[4 * i + 1] + u.z * x[4 * i + 2] + u.w * x[4 * i + 3];
+                        acc[r] += v.x * x[4 * i + 128] + v.y * x[4 * i + 129] + v.z * x[4 * i + 130] + v.w * x[4 * i + 131];
+                    }
+                }
+            }
+            for (; i < n4; i += 32) {
+                const float4 u = w4[i];
+#pragma unroll
+                for (int r = 0; r < 4; ++r)
+                    if (r < R) {
+                        const float* x = rows + (size_t)r * width;
+                        acc[r] += u.x * x[4 * i] + u.y * x[4 * i + 1] + u.z * x[4 * i + 2] + u.w * x[4 * i + 3];
+                    }
+            }
+        } else {
+            for (int i = lane; i < width; i += 32) {
+                const float u = wr[i];
+#pragma unroll
+                for (int r = 0; r < 4; ++r)
+                    if (r < R) acc[r] += u * rows[(size_t)r * width + i];
+            }
+        }
+#pragma unroll
+        for (int r = 0; r < 4; ++r) {
+            const float v = warp_sum(acc[r]);
+            if (lane == 0 && r < R) logits[(size_t)r * experts + e] = v;
+        }
     }
     __syncthreads();
-    if (warp != 0) return;
-    __syncwarp();
+    if (warp >= R) return;
+    const int r = r0 + warp;
+    float* s = logits + (size_t)warp * experts;
     // The choice goes by the logits: scores are monotone in them, and a sigmoid that has reached 1 in 32-bit would tie.
     float m = -INFINITY, l = 1.f;
     if (softmax_scores) {
@@ -504,15 +543,17 @@ extern "C" int imparo_moe_route(const void* h, int dtype, const float* w_r, int 
                                 int softmax_scores, int renormalise, int* ids, float* wts, cudaStream_t stream) {
     if (n_rows <= 0) return 0;
     if (top < 1 || top > experts || top > 32 || experts > 2048) return -2;
-    const size_t smem = (size_t)(width + experts) * sizeof(float);
+    int per = 4;
+    if ((size_t)4 * (width + experts) * sizeof(float) > 48 * 1024) per = 1;
+    const size_t smem = (size_t)per * (width + experts) * sizeof(float);
     if (smem > 48 * 1024) return -25;
-    dim3 grid(n_rows);
+    dim3 grid((n_rows + per - 1) / per);
     if (dtype == IMPARO_DT_F32)
-        launch(moe_route_kernel<float>, grid, dim3(128), smem, stream, (const float*)h, w_r, n_rows, width, experts, top,
-               softmax_scores, renormalise, ids, wts);
+        launch(moe_route_kernel<float>, grid, dim3(256), smem, stream, (const float*)h, w_r, n_rows, width, experts, top,
+               softmax_scores, renormalise, per, ids, wts);
     else if (dtype == IMPARO_DT_BF16)
-        launch(moe_route_kernel<__nv_bfloat16>, grid, dim3(128), smem, stream, (const __nv_bfloat16*)h, w_r, n_rows, width, experts,
-               top, softmax_scores, renormalise, ids, wts);
+        launch(moe_route_kernel<__nv_bfloat16>, grid, dim3(256), smem, stream, (const __nv_bfloat16*)h, w_r, n_rows, width, experts,
+               top, softmax_scores, renormalise, per, ids, wts);
     else return -1;
     IMPARO_CHECK_LAUNCH();
     return 0;
