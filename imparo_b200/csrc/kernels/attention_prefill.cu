@@ -726,7 +726,19 @@ extern "C" int imparo_attention_decode_mma(const void* q, const void* k_cache, c
                                            const int* table, int max_blocks, int page_size, int n_pages,
                                            int window, float scale, void* out, float* part_acc, float* part_ml,
                                            int n_tok, int nh, int nkv, int hd, int chunk, int n_splits, int fresh,
-                                           int overlap_prev, float softcap, int* status, cudaStream_t stream) {
+                                           int overlap_prev, int* status, cudaStream_t stream) {
+    return decode_mma_launch(q, nullptr, k_cache, v_cache, positions, item_of_token, table, max_blocks, page_size, n_pages, window,
+                             scale, out, part_acc, part_ml, n_tok, nh, nkv, hd, chunk, n_splits, fresh, overlap_prev ? 1 : 0,
+                             status, stream);
+}
+
+// The same with a soft cap c > 0 on the scaled scores: c * tanh(score / c).
+extern "C" int imparo_attention_decode_mma_capped(const void* q, const void* k_cache, const void* v_cache,
+                                                  const int* positions, const int* item_of_token,
+                                                  const int* table, int max_blocks, int page_size, int n_pages,
+                                                  int window, float scale, void* out, float* part_acc, float* part_ml,
+                                                  int n_tok, int nh, int nkv, int hd, int chunk, int n_splits, int fresh,
+                                                  int overlap_prev, float softcap, int* status, cudaStream_t stream) {
     return decode_mma_launch(q, nullptr, k_cache, v_cache, positions, item_of_token, table, max_blocks, page_size, n_pages, window,
                              scale, out, part_acc, part_ml, n_tok, nh, nkv, hd, chunk, n_splits, fresh, overlap_prev ? 1 : 0,
                              status, stream, softcap);

@@ -5,8 +5,8 @@
 //      portion's first row come from the slot's conv state (the last taps-1 inputs, oldest first), zeros for a
 //      fresh request (the slot is cleared).  The same launch makes the step sizes dt = softplus(dt + dt_bias) in
 //      32-bit.  A second small kernel then moves the conv state on (it runs after every reader of the old state).
-//  (2) mamba2_scan: per request, head and 32 value columns one warp walks the rows in order with the state column
-//      S[:, p] in registers:  S = exp(-exp(A_log) dt) S + dt B x[p];  y[p] = C . S + D x[p].  Decays, step sizes
+//  (2) mamba2_scan: per request, head and 32 value columns one to four warps walk the rows in order with the state column
+//      S[:, p] in their registers (a stretch each):  S = exp(-exp(A_log) dt) S + dt B x[p];  y[p] = C . S + D x[p].  Decays, step sizes
 //      and the state are 32-bit in both precisions.
 //  (3) Long portions run in chunks of L rows side by side (three launches, as the decayed linear attention does):
 //      every chunk's own state from zero and its total decay; a scan over each request's chunks that leaves every
@@ -116,20 +116,22 @@ __device__ __forceinline__ void state_step_no_out(float (&S)[NMAX], const float*
     }
 }
 
-// A row's B and C entries of this lane (n = lane, lane + 32, ...), its step size and its x value, fetched one row ahead
-// of the row being computed, so that their latency hides behind the arithmetic.
-template <int NMAX>
+// A row's B and C entries of this lane within its warp's share of the state (n = n0 + lane, n0 + lane + 32, ...), its step
+// size and its x value, fetched one row ahead of the row being computed, so that their latency hides behind the arithmetic.
+template <int NH>
 struct RowAhead {
-    static constexpr int PER = (NMAX + 31) / 32;
+    static constexpr int PER = (NH + 31) / 32;
     float b[PER], c[PER], step, x;
-    __device__ __forceinline__ void fetch(const float* __restrict__ xbc, const float* __restrict__ dt, int t, int channels, int inner,
-                                          int b_off, int c_off, int x_col, int heads, int h, int N, int lane, bool live, bool want_c) {
+    __device__ __forceinline__ void fetch(const float* __restrict__ xbc, const float* __restrict__ dt, int t, int channels,
+                                          int b_off, int c_off, int x_col, int heads, int h, int n0, int N, int lane, bool live,
+                                          bool want_c) {
         const float* row = xbc + (size_t)t * channels;
 #pragma unroll
         for (int i = 0; i < PER; ++i) {
-            const int n = lane + 32 * i;
-            b[i] = n < N ? row[b_off + n] : 0.f;
-            c[i] = (want_c && n < N) ? row[c_off + n] : 0.f;
+            const int n = n0 + lane + 32 * i;
+            const bool in = lane + 32 * i < NH && n < N;
+            b[i] = in ? row[b_off + n] : 0.f;
+            c[i] = (want_c && in) ? row[c_off + n] : 0.f;
         }
         step = dt[(size_t)t * heads + h];
         x = live ? row[x_col] : 0.f;
@@ -138,21 +140,24 @@ struct RowAhead {
 #pragma unroll
         for (int i = 0; i < PER; ++i) {
             const int n = lane + 32 * i;
-            if (n < NMAX) { bs[n] = b[i]; if (cs) cs[n] = c[i]; }
+            if (n < NH) { bs[n] = b[i]; if (cs) cs[n] = c[i]; }
         }
     }
 };
 
-// grid (heads, items, ceil(vdim / 32)), one warp each
-template <int NMAX>
-__global__ void __launch_bounds__(32)
+// The state column S[:, p] of a (request, head, value column) is cut into SPLIT stretches of NH entries, one warp each
+// (fewer registers per thread, more warps per SM); the warps' shares of C . S meet in shared memory, added in warp order.
+// grid (heads, items, ceil(vdim / 32)), SPLIT warps
+template <int NH, int SPLIT>
+__global__ void __launch_bounds__(32 * SPLIT, SPLIT == 1 ? 16 : (SPLIT == 2 ? 8 : 4))
 mamba2_scan_kernel(const float* __restrict__ xbc, const float* __restrict__ dt, const float* __restrict__ A_log,
                    const float* __restrict__ D, float* __restrict__ state, const int* __restrict__ item_row_start,
                    const int* __restrict__ item_slot, int n_slots, float* __restrict__ y,
                    int heads, int vdim, int N, int groups, int* status) {
-    __shared__ __align__(16) float bc[2][NMAX];
+    __shared__ __align__(16) float bc[SPLIT][2][NH];
+    __shared__ float part[2][SPLIT][32];
     pdl_trigger();
-    const int h = blockIdx.x, item = blockIdx.y, lane = threadIdx.x;
+    const int h = blockIdx.x, item = blockIdx.y, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int p = blockIdx.z * 32 + lane;
     const int first = item_row_start[item], last = item_row_start[item + 1];
     const int slot = item_slot[item];
@@ -160,32 +165,41 @@ mamba2_scan_kernel(const float* __restrict__ xbc, const float* __restrict__ dt, 
     const float d_skip = D[h];
     pdl_wait();
     if (slot < 0 || slot >= n_slots) {
-        if (lane == 0 && blockIdx.z == 0 && h == 0) report(status, IMPARO_ST_SLOT_RANGE, 62, item, slot);
+        if (threadIdx.x == 0 && blockIdx.z == 0 && h == 0) report(status, IMPARO_ST_SLOT_RANGE, 62, item, slot);
         return;
     }
     const int inner = heads * vdim, channels = inner + 2 * groups * N;
     const int g = h / (heads / groups);
     const bool live = p < vdim;
+    const int n0 = warp * NH;
     float* sp = state + (((size_t)slot * heads + h) * N) * vdim + p;
-    float S[NMAX];
+    float S[NH];
 #pragma unroll
-    for (int n = 0; n < NMAX; ++n) S[n] = (live && n < N) ? sp[(size_t)n * vdim] : 0.f;
-    RowAhead<NMAX> next;
+    for (int n = 0; n < NH; ++n) S[n] = (live && n0 + n < N) ? sp[(size_t)(n0 + n) * vdim] : 0.f;
+    RowAhead<NH> next;
     const int b_off = inner + g * N, c_off = inner + groups * N + g * N, x_col = h * vdim + p;
-    if (first < last) next.fetch(xbc, dt, first, channels, inner, b_off, c_off, x_col, heads, h, N, lane, live, true);
+    if (first < last) next.fetch(xbc, dt, first, channels, b_off, c_off, x_col, heads, h, n0, N, lane, live, true);
     for (int t = first; t < last; ++t) {
         __syncwarp();
-        next.put(bc[0], bc[1], lane);
+        next.put(bc[warp][0], bc[warp][1], lane);
         __syncwarp();
         const float step = next.step, xv = next.x;
-        if (t + 1 < last) next.fetch(xbc, dt, t + 1, channels, inner, b_off, c_off, x_col, heads, h, N, lane, live, true);
-        const float acc = state_step<NMAX>(S, bc[0], bc[1], expf(a * step), step * xv);
-        if (live) y[(size_t)t * inner + h * vdim + p] = acc + d_skip * xv;
+        if (t + 1 < last) next.fetch(xbc, dt, t + 1, channels, b_off, c_off, x_col, heads, h, n0, N, lane, live, true);
+        float acc = state_step<NH>(S, bc[warp][0], bc[warp][1], expf(a * step), step * xv);
+        if (SPLIT > 1) {
+            const int buf = (t - first) & 1;
+            part[buf][warp][lane] = acc;
+            __syncthreads();
+            acc = part[buf][0][lane];
+#pragma unroll
+            for (int w = 1; w < SPLIT; ++w) acc += part[buf][w][lane];
+        }
+        if (warp == 0 && live) y[(size_t)t * inner + h * vdim + p] = acc + d_skip * xv;
     }
     if (live) {
 #pragma unroll
-        for (int n = 0; n < NMAX; ++n)
-            if (n < N) sp[(size_t)n * vdim] = S[n];
+        for (int n = 0; n < NH; ++n)
+            if (n0 + n < N) sp[(size_t)(n0 + n) * vdim] = S[n];
     }
 }
 
@@ -211,15 +225,15 @@ __global__ void mamba2_chunk_plan_kernel(const int* __restrict__ item_row_start,
 }
 
 // every chunk's own state from zero [chunk, heads, N, vdim] and the chunk's total decay [chunk, heads]
-template <int NMAX>
-__global__ void __launch_bounds__(32)
+template <int NH, int SPLIT>
+__global__ void __launch_bounds__(32 * SPLIT, SPLIT == 1 ? 16 : (SPLIT == 2 ? 8 : 4))
 mamba2_chunk_state_kernel(const float* __restrict__ xbc, const float* __restrict__ dt, const float* __restrict__ A_log,
                           const int* __restrict__ chunk_lo, const int* __restrict__ chunk_hi,
                           float* __restrict__ chunk_state, float* __restrict__ chunk_decay,
                           int heads, int vdim, int N, int groups) {
-    __shared__ __align__(16) float bs[NMAX];
+    __shared__ __align__(16) float bs[SPLIT][NH];
     pdl_trigger();
-    const int h = blockIdx.x, c = blockIdx.y, lane = threadIdx.x;
+    const int h = blockIdx.x, c = blockIdx.y, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int p = blockIdx.z * 32 + lane;
     const float a = -expf(A_log[h]);
     pdl_wait();
@@ -228,29 +242,30 @@ mamba2_chunk_state_kernel(const float* __restrict__ xbc, const float* __restrict
     const int inner = heads * vdim, channels = inner + 2 * groups * N;
     const int g = h / (heads / groups);
     const bool live = p < vdim;
-    float S[NMAX];
+    const int n0 = warp * NH;
+    float S[NH];
 #pragma unroll
-    for (int n = 0; n < NMAX; ++n) S[n] = 0.f;
+    for (int n = 0; n < NH; ++n) S[n] = 0.f;
     float total = 0.f;                                            // sum of a * dt over the chunk
-    RowAhead<NMAX> next;
+    RowAhead<NH> next;
     const int b_off = inner + g * N, x_col = h * vdim + p;
-    next.fetch(xbc, dt, lo, channels, inner, b_off, 0, x_col, heads, h, N, lane, live, false);
+    next.fetch(xbc, dt, lo, channels, b_off, 0, x_col, heads, h, n0, N, lane, live, false);
     for (int t = lo; t < hi; ++t) {
         __syncwarp();
-        next.put(bs, nullptr, lane);
+        next.put(bs[warp], nullptr, lane);
         __syncwarp();
         const float step = next.step, xv = next.x;
-        if (t + 1 < hi) next.fetch(xbc, dt, t + 1, channels, inner, b_off, 0, x_col, heads, h, N, lane, live, false);
+        if (t + 1 < hi) next.fetch(xbc, dt, t + 1, channels, b_off, 0, x_col, heads, h, n0, N, lane, live, false);
         total += a * step;
-        state_step_no_out<NMAX>(S, bs, expf(a * step), step * xv);
+        state_step_no_out<NH>(S, bs[warp], expf(a * step), step * xv);
     }
     if (live) {
         float* out = chunk_state + (((size_t)c * heads + h) * N) * vdim + p;
 #pragma unroll
-        for (int n = 0; n < NMAX; ++n)
-            if (n < N) out[(size_t)n * vdim] = S[n];
+        for (int n = 0; n < NH; ++n)
+            if (n0 + n < N) out[(size_t)(n0 + n) * vdim] = S[n];
     }
-    if (lane == 0 && blockIdx.z == 0) chunk_decay[(size_t)c * heads + h] = total;
+    if (threadIdx.x == 0 && blockIdx.z == 0) chunk_decay[(size_t)c * heads + h] = total;
 }
 
 // per request and head: chunk_state[c] becomes the state BEFORE chunk c; the slot gets the state after the last chunk
@@ -296,15 +311,16 @@ mamba2_chunk_scan_kernel(float* __restrict__ chunk_state, const float* __restric
 }
 
 // every chunk's outputs: the recurrence inside the chunk from its starting state (chunks side by side)
-template <int NMAX>
-__global__ void __launch_bounds__(32)
+template <int NH, int SPLIT>
+__global__ void __launch_bounds__(32 * SPLIT, SPLIT == 1 ? 16 : (SPLIT == 2 ? 8 : 4))
 mamba2_chunk_out_kernel(const float* __restrict__ xbc, const float* __restrict__ dt, const float* __restrict__ A_log,
                         const float* __restrict__ D, const int* __restrict__ chunk_lo, const int* __restrict__ chunk_hi,
                         const float* __restrict__ chunk_state, float* __restrict__ y,
                         int heads, int vdim, int N, int groups) {
-    __shared__ __align__(16) float bc[2][NMAX];
+    __shared__ __align__(16) float bc[SPLIT][2][NH];
+    __shared__ float part[2][SPLIT][32];
     pdl_trigger();
-    const int h = blockIdx.x, c = blockIdx.y, lane = threadIdx.x;
+    const int h = blockIdx.x, c = blockIdx.y, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int p = blockIdx.z * 32 + lane;
     const float a = -expf(A_log[h]);
     const float d_skip = D[h];
@@ -314,21 +330,30 @@ mamba2_chunk_out_kernel(const float* __restrict__ xbc, const float* __restrict__
     const int inner = heads * vdim, channels = inner + 2 * groups * N;
     const int g = h / (heads / groups);
     const bool live = p < vdim;
+    const int n0 = warp * NH;
     const float* sp = chunk_state + (((size_t)c * heads + h) * N) * vdim + p;
-    float S[NMAX];
+    float S[NH];
 #pragma unroll
-    for (int n = 0; n < NMAX; ++n) S[n] = (live && n < N) ? sp[(size_t)n * vdim] : 0.f;
-    RowAhead<NMAX> next;
+    for (int n = 0; n < NH; ++n) S[n] = (live && n0 + n < N) ? sp[(size_t)(n0 + n) * vdim] : 0.f;
+    RowAhead<NH> next;
     const int b_off = inner + g * N, c_off = inner + groups * N + g * N, x_col = h * vdim + p;
-    next.fetch(xbc, dt, lo, channels, inner, b_off, c_off, x_col, heads, h, N, lane, live, true);
+    next.fetch(xbc, dt, lo, channels, b_off, c_off, x_col, heads, h, n0, N, lane, live, true);
     for (int t = lo; t < hi; ++t) {
         __syncwarp();
-        next.put(bc[0], bc[1], lane);
+        next.put(bc[warp][0], bc[warp][1], lane);
         __syncwarp();
         const float step = next.step, xv = next.x;
-        if (t + 1 < hi) next.fetch(xbc, dt, t + 1, channels, inner, b_off, c_off, x_col, heads, h, N, lane, live, true);
-        const float acc = state_step<NMAX>(S, bc[0], bc[1], expf(a * step), step * xv);
-        if (live) y[(size_t)t * inner + h * vdim + p] = acc + d_skip * xv;
+        if (t + 1 < hi) next.fetch(xbc, dt, t + 1, channels, b_off, c_off, x_col, heads, h, n0, N, lane, live, true);
+        float acc = state_step<NH>(S, bc[warp][0], bc[warp][1], expf(a * step), step * xv);
+        if (SPLIT > 1) {
+            const int buf = (t - lo) & 1;
+            part[buf][warp][lane] = acc;
+            __syncthreads();
+            acc = part[buf][0][lane];
+#pragma unroll
+            for (int w = 1; w < SPLIT; ++w) acc += part[buf][w][lane];
+        }
+        if (warp == 0 && live) y[(size_t)t * inner + h * vdim + p] = acc + d_skip * xv;
     }
 }
 
@@ -391,13 +416,14 @@ extern "C" int imparo_mamba2_conv(const void* proj, int dtype, long long stride,
     return 0;
 }
 
+// state entries per warp, warps per state column
 #define MAMBA2_BY_N(CALL)                                       \
     do {                                                        \
-        if (N <= 16) { CALL(16); }                              \
-        else if (N <= 32) { CALL(32); }                         \
-        else if (N <= 64) { CALL(64); }                         \
-        else if (N <= 128) { CALL(128); }                       \
-        else { CALL(256); }                                     \
+        if (N <= 16) { CALL(16, 1); }                           \
+        else if (N <= 32) { CALL(32, 1); }                      \
+        else if (N <= 64) { CALL(32, 2); }                      \
+        else if (N <= 128) { CALL(64, 2); }                     \
+        else { CALL(64, 4); }                                   \
     } while (0)
 
 extern "C" int imparo_mamba2_scan(const float* xbc, const float* dt, const float* A_log, const float* D, float* state,
@@ -407,8 +433,8 @@ extern "C" int imparo_mamba2_scan(const float* xbc, const float* dt, const float
     if (N < 1 || N > 256) return -3;
     if (groups < 1 || heads % groups) return -5;
     dim3 grid(heads, n_items, (vdim + 31) / 32);
-#define CALL(NM) launch(mamba2_scan_kernel<NM>, grid, dim3(32), 0, stream, xbc, dt, A_log, D, state, item_row_start, item_slot, \
-                        n_slots, y, heads, vdim, N, groups, status)
+#define CALL(NH, SP) launch(mamba2_scan_kernel<NH, SP>, grid, dim3(32 * SP), 0, stream, xbc, dt, A_log, D, state, item_row_start, \
+                            item_slot, n_slots, y, heads, vdim, N, groups, status)
     MAMBA2_BY_N(CALL);
 #undef CALL
     IMPARO_CHECK_LAUNCH();
@@ -433,8 +459,8 @@ extern "C" int imparo_mamba2_scan_chunked(const float* xbc, const float* dt, con
            chunk_hi, item_chunk_start);
     IMPARO_CHECK_LAUNCH();
     dim3 grid(heads, max_chunks, (vdim + 31) / 32);
-#define CALL(NM) launch(mamba2_chunk_state_kernel<NM>, grid, dim3(32), 0, stream, xbc, dt, A_log, (const int*)chunk_lo, \
-                        (const int*)chunk_hi, chunk_state, chunk_decay, heads, vdim, N, groups)
+#define CALL(NH, SP) launch(mamba2_chunk_state_kernel<NH, SP>, grid, dim3(32 * SP), 0, stream, xbc, dt, A_log, (const int*)chunk_lo, \
+                            (const int*)chunk_hi, chunk_state, chunk_decay, heads, vdim, N, groups)
     MAMBA2_BY_N(CALL);
 #undef CALL
     IMPARO_CHECK_LAUNCH();
@@ -442,8 +468,8 @@ extern "C" int imparo_mamba2_scan_chunked(const float* xbc, const float* dt, con
     launch(mamba2_chunk_scan_kernel, dim3(heads, n_items, (per + 255) / 256), dim3(256), 0, stream, chunk_state,
            (const float*)chunk_decay, (const int*)item_chunk_start, item_slot, n_slots, state, heads, vdim, N, status);
     IMPARO_CHECK_LAUNCH();
-#define CALL(NM) launch(mamba2_chunk_out_kernel<NM>, grid, dim3(32), 0, stream, xbc, dt, A_log, D, (const int*)chunk_lo, \
-                        (const int*)chunk_hi, (const float*)chunk_state, y, heads, vdim, N, groups)
+#define CALL(NH, SP) launch(mamba2_chunk_out_kernel<NH, SP>, grid, dim3(32 * SP), 0, stream, xbc, dt, A_log, D, (const int*)chunk_lo, \
+                            (const int*)chunk_hi, (const float*)chunk_state, y, heads, vdim, N, groups)
     MAMBA2_BY_N(CALL);
 #undef CALL
     IMPARO_CHECK_LAUNCH();

@@ -782,7 +782,7 @@ def paged_attention_split(q, k_cache, v_cache, positions, item_of_token, table, 
           "paged_attention_split: chunk * n_splits must cover every position the block table can hold")
     if use_mma:
         # bfloat16, head 64/128: the tensor-core version (the scalar one is bound by instruction issue)
-        rc = _lib.kernels().imparo_attention_decode_mma(
+        rc = _lib.kernels().imparo_attention_decode_mma_capped(
             _ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(positions), _ptr(item_of_token), _ptr(table),
             table.shape[1], page_size, n_pages, int(window or 0), float(scale), _ptr(out), _ptr(part_acc), _ptr(part_ml),
             T, nh, nkv, hd, int(chunk), int(n_splits), int(fresh), int(bool(overlap_prev)), float(softcap or 0.0), _ptr(status),
