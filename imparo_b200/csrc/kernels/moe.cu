@@ -1,8 +1,8 @@
 // A routed feed-forward (mixture of experts) over the rows of a step.
 //
-//  (1) moe_route: router logits z = W_r h in 32-bit (one warp per row), score = sigmoid(z) or softmax(z), the `top`
-//      largest scores (ties: the lower expert), optionally renormalised to sum 1.  Leaves expert ids [rows, top] and
-//      weights [rows, top].
+//  (1) moe_route: router logits z = W_r h in 32-bit (a warp per expert, four rows per block), then a warp per row picks the
+//      `top` largest (by logit: the scores sigmoid(z) or softmax(z) are monotone in it; ties: the lower expert), optionally
+//      renormalised to sum 1.  Leaves expert ids [rows, top] and weights [rows, top].
 //  (2) moe_rows_*: each (row, choice) pair on its own: the expert's gate and up rows times the (optionally weighted)
 //      input, silu(gate) * up, then the expert's down rows; the choices of a row are added in order.  Weights are
 //      streamed once per pair: the form for steps of few rows.
@@ -67,68 +67,80 @@ __device__ __forceinline__ float warp_dot(const T* __restrict__ w, const float* 
 }
 
 // ---- (1) router -------------------------------------------------------------------------------------------------
-// A block takes up to four rows, so that a router row read once serves them all; a warp per expert in turn; warp r then
-// picks for row r.  A dot product always adds in the same order, whatever else the launch holds.
+// Logits: a block takes up to four rows (a router row read once serves them all) and eight experts, a warp each; grid
+// (row blocks, ceil(experts / 8)).  A dot product always adds in the same order, whatever else the launch holds.
 template <typename T>
 __global__ void __launch_bounds__(256)
-moe_route_kernel(const T* __restrict__ h, const float* __restrict__ w_r, int n_rows, int width, int experts, int top,
-                 int softmax_scores, int renormalise, int rows_per_block, int* __restrict__ ids, float* __restrict__ wts) {
-    extern __shared__ __align__(16) float route_smem[];  // [rows][width] the rows in 32-bit, then [rows][experts] logits
+moe_logits_kernel(const T* __restrict__ h, const float* __restrict__ w_r, int n_rows, int width, int experts, int rows_per_block,
+                  float* __restrict__ logits) {
+    extern __shared__ __align__(16) float route_smem[];  // [rows][width] the rows in 32-bit
     pdl_trigger();
     pdl_wait();
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int r0 = blockIdx.x * rows_per_block;
     const int R = min(rows_per_block, n_rows - r0);
     float* rows = route_smem;
-    float* logits = route_smem + (size_t)rows_per_block * width;
     for (int i = threadIdx.x; i < R * width; i += blockDim.x) rows[i] = to_f32(h[(size_t)r0 * width + i]);
     __syncthreads();
-    const bool vec = width % 4 == 0;
-    for (int e = warp; e < experts; e += 8) {
-        const float* wr = w_r + (size_t)e * width;
-        float acc[4] = {0.f, 0.f, 0.f, 0.f};
-        if (vec) {
-            const float4* w4 = reinterpret_cast<const float4*>(wr);
-            const int n4 = width / 4;
-            int i = lane;
-            for (; i + 32 < n4; i += 64) {                   // two loads in flight
-                const float4 u = w4[i], v = w4[i + 32];
+    const int e = blockIdx.y * 8 + warp;
+    if (e >= experts) return;
+    const float* wr = w_r + (size_t)e * width;
+    float acc[4] = {0.f, 0.f, 0.f, 0.f};
+    if (width % 4 == 0) {
+        const float4* w4 = reinterpret_cast<const float4*>(wr);
+        const int n4 = width / 4;
+        int i = lane;
+        for (; i + 96 < n4; i += 128) {                      // four loads in flight
+            float4 u[4];
 #pragma unroll
-                for (int r = 0; r < 4; ++r) {
-                    if (r < R) {
-                        const float* x = rows + (size_t)r * width;
-                        acc[r] += u.x * x[4 * i] + u.y * x[4 * i + 1] + u.z * x[4 * i + 2] + u.w * x[4 * i + 3];
-                        acc[r] += v.x * x[4 * i + 128] + v.y * x[4 * i + 129] + v.z * x[4 * i + 130] + v.w * x[4 * i + 131];
-                    }
+            for (int k = 0; k < 4; ++k) u[k] = w4[i + 32 * k];
+#pragma unroll
+            for (int r = 0; r < 4; ++r) {
+                if (r < R) {
+                    const float* x = rows + (size_t)r * width + 4 * i;
+#pragma unroll
+                    for (int k = 0; k < 4; ++k)
+                        acc[r] += u[k].x * x[128 * k] + u[k].y * x[128 * k + 1] + u[k].z * x[128 * k + 2] + u[k].w * x[128 * k + 3];
                 }
             }
-            for (; i < n4; i += 32) {
-                const float4 u = w4[i];
-#pragma unroll
-                for (int r = 0; r < 4; ++r)
-                    if (r < R) {
-                        const float* x = rows + (size_t)r * width;
-                        acc[r] += u.x * x[4 * i] + u.y * x[4 * i + 1] + u.z * x[4 * i + 2] + u.w * x[4 * i + 3];
-                    }
-            }
-        } else {
-            for (int i = lane; i < width; i += 32) {
-                const float u = wr[i];
-#pragma unroll
-                for (int r = 0; r < 4; ++r)
-                    if (r < R) acc[r] += u * rows[(size_t)r * width + i];
-            }
         }
+        for (; i < n4; i += 32) {
+            const float4 u = w4[i];
 #pragma unroll
-        for (int r = 0; r < 4; ++r) {
-            const float v = warp_sum(acc[r]);
-            if (lane == 0 && r < R) logits[(size_t)r * experts + e] = v;
+            for (int r = 0; r < 4; ++r)
+                if (r < R) {
+                    const float* x = rows + (size_t)r * width + 4 * i;
+                    acc[r] += u.x * x[0] + u.y * x[1] + u.z * x[2] + u.w * x[3];
+                }
+        }
+    } else {
+        for (int i = lane; i < width; i += 32) {
+            const float u = wr[i];
+#pragma unroll
+            for (int r = 0; r < 4; ++r)
+                if (r < R) acc[r] += u * rows[(size_t)r * width + i];
         }
     }
-    __syncthreads();
-    if (warp >= R) return;
-    const int r = r0 + warp;
-    float* s = logits + (size_t)warp * experts;
+#pragma unroll
+    for (int r = 0; r < 4; ++r) {
+        const float v = warp_sum(acc[r]);
+        if (lane == 0 && r < R) logits[(size_t)(r0 + r) * experts + e] = v;
+    }
+}
+
+// The choice: a warp per row, four rows per block
+__global__ void __launch_bounds__(128)
+moe_pick_kernel(const float* __restrict__ logits, int n_rows, int experts, int top, int softmax_scores, int renormalise,
+                int* __restrict__ ids, float* __restrict__ wts) {
+    extern __shared__ __align__(16) float pick_smem[];   // [4][experts]
+    pdl_trigger();
+    pdl_wait();
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int r = blockIdx.x * 4 + warp;
+    if (r >= n_rows) return;
+    float* s = pick_smem + (size_t)warp * experts;
+    for (int e = lane; e < experts; e += 32) s[e] = logits[(size_t)r * experts + e];
+    __syncwarp();
     // The choice goes by the logits: scores are monotone in them, and a sigmoid that has reached 1 in 32-bit would tie.
     float m = -INFINITY, l = 1.f;
     if (softmax_scores) {
@@ -165,6 +177,39 @@ moe_route_kernel(const T* __restrict__ h, const float* __restrict__ w_r, int n_r
 }
 
 // ---- (2) pair by pair ---------------------------------------------------------------------------------------------
+// two rows against the same vector at once: eight loads in flight
+template <typename T>
+__device__ __forceinline__ void warp_dot2(const T* __restrict__ w0, const T* __restrict__ w1, const float* __restrict__ x, int n,
+                                          bool vec, int lane, float& r0, float& r1) {
+    if (!vec) {
+        r0 = warp_dot<T>(w0, x, n, false, lane);
+        r1 = warp_dot<T>(w1, x, n, false, lane);
+        return;
+    }
+    constexpr int PER = Vec16<T>::N;
+    const uint4* p0 = reinterpret_cast<const uint4*>(w0);
+    const uint4* p1 = reinterpret_cast<const uint4*>(w1);
+    const int n4 = n / PER;
+    int i = lane;
+    float a[4] = {0.f, 0.f, 0.f, 0.f}, b[4] = {0.f, 0.f, 0.f, 0.f};
+    for (; i + 96 < n4; i += 128) {
+        uint4 u[4], v[4];
+#pragma unroll
+        for (int k = 0; k < 4; ++k) { u[k] = p0[i + 32 * k]; v[k] = p1[i + 32 * k]; }
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            a[k] += dot16<T>(u[k], x + (size_t)(i + 32 * k) * PER);
+            b[k] += dot16<T>(v[k], x + (size_t)(i + 32 * k) * PER);
+        }
+    }
+    for (; i < n4; i += 32) {
+        a[0] += dot16<T>(p0[i], x + (size_t)i * PER);
+        b[0] += dot16<T>(p1[i], x + (size_t)i * PER);
+    }
+    r0 = warp_sum((a[0] + a[1]) + (a[2] + a[3]));
+    r1 = warp_sum((b[0] + b[1]) + (b[2] + b[3]));
+}
+
 // grid (rows * top, ceil(ff / 32)); 8 warps, each 4 features
 template <typename T>
 __global__ void __launch_bounds__(256)
@@ -186,8 +231,8 @@ moe_rows_up_kernel(const T* __restrict__ h, const T* __restrict__ w_gu, const in
     for (int j = 0; j < 4; ++j) {
         const int f = blockIdx.y * 32 + warp * 4 + j;
         if (f >= ff) break;
-        const float ag = warp_dot<T>(base + (size_t)f * width, up_smem, width, vec, lane);
-        const float au = warp_dot<T>(base + (size_t)(ff + f) * width, up_smem, width, vec, lane);
+        float ag, au;
+        warp_dot2<T>(base + (size_t)f * width, base + (size_t)(ff + f) * width, up_smem, width, vec, lane, ag, au);
         if (lane == 0) mid[(size_t)pair * ff + f] = from_f32<T>(silu(ag) * au);
     }
 }
@@ -539,22 +584,25 @@ moe_tile_sum_kernel(const float* __restrict__ out_g, const int* __restrict__ slo
 
 using namespace imparo;
 
+// logits: float32 scratch [n_rows, experts].  Two launches.
 extern "C" int imparo_moe_route(const void* h, int dtype, const float* w_r, int n_rows, int width, int experts, int top,
-                                int softmax_scores, int renormalise, int* ids, float* wts, cudaStream_t stream) {
+                                int softmax_scores, int renormalise, float* logits, int* ids, float* wts, cudaStream_t stream) {
     if (n_rows <= 0) return 0;
-    if (top < 1 || top > experts || top > 32 || experts > 2048) return -2;
+    if (top < 1 || top > experts || top > 32 || experts > 2048 || logits == nullptr) return -2;
     int per = 4;
-    if ((size_t)4 * (width + experts) * sizeof(float) > 48 * 1024) per = 1;
-    const size_t smem = (size_t)per * (width + experts) * sizeof(float);
+    if ((size_t)4 * width * sizeof(float) > 48 * 1024) per = 1;
+    const size_t smem = (size_t)per * width * sizeof(float);
     if (smem > 48 * 1024) return -25;
-    dim3 grid((n_rows + per - 1) / per);
+    dim3 grid((n_rows + per - 1) / per, (experts + 7) / 8);
     if (dtype == IMPARO_DT_F32)
-        launch(moe_route_kernel<float>, grid, dim3(256), smem, stream, (const float*)h, w_r, n_rows, width, experts, top,
-               softmax_scores, renormalise, per, ids, wts);
+        launch(moe_logits_kernel<float>, grid, dim3(256), smem, stream, (const float*)h, w_r, n_rows, width, experts, per, logits);
     else if (dtype == IMPARO_DT_BF16)
-        launch(moe_route_kernel<__nv_bfloat16>, grid, dim3(256), smem, stream, (const __nv_bfloat16*)h, w_r, n_rows, width, experts,
-               top, softmax_scores, renormalise, per, ids, wts);
+        launch(moe_logits_kernel<__nv_bfloat16>, grid, dim3(256), smem, stream, (const __nv_bfloat16*)h, w_r, n_rows, width, experts,
+               per, logits);
     else return -1;
+    IMPARO_CHECK_LAUNCH();
+    launch(moe_pick_kernel, dim3((n_rows + 3) / 4), dim3(128), (size_t)4 * experts * sizeof(float), stream, (const float*)logits, n_rows,
+           experts, top, softmax_scores, renormalise, ids, wts);
     IMPARO_CHECK_LAUNCH();
     return 0;
 }

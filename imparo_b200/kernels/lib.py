@@ -125,7 +125,7 @@ def _declare_kernels(lib):
     _declare(lib, "imparo_mamba2_scan", [P, P, P, P, P, P, P, I, I, P, I, I, I, I, P, S])
     _declare(lib, "imparo_mamba2_scan_chunked", [P, P, P, P, P, P, P, I, I, P, I, I, I, I, I, I, P, P, P, P, S])
     _declare(lib, "imparo_gate_group_rmsnorm", [P, P, I, c_int64, P, c_float, P, I, I, I, I, S])
-    _declare(lib, "imparo_moe_route", [P, I, P, I, I, I, I, I, I, P, P, S])
+    _declare(lib, "imparo_moe_route", [P, I, P, I, I, I, I, I, I, P, P, P, S])
     _declare(lib, "imparo_moe_rows", [P, P, P, I, P, P, I, I, I, I, I, I, P, P, S])
     _declare(lib, "imparo_moe_tiles", [P, P, P, P, P, I, I, I, I, I, I, P, P, P, P, P, P, S])
     _declare(lib, "imparo_moe_grouped", [P, P, P, I, P, P, I, I, I, I, I, I, P, P, P, P, S])

@@ -1285,17 +1285,21 @@ def gate_group_rmsnorm(y: torch.Tensor, z: torch.Tensor, w: torch.Tensor, eps: f
 
 # ---- routed feed-forward (csrc/kernels/moe.cu) -------------------------------------------------------------------
 def moe_route(h: torch.Tensor, w_router: torch.Tensor, top: int, ids: torch.Tensor, wts: torch.Tensor, softmax: bool = False,
-              renormalise: bool = False) -> None:
+              renormalise: bool = False, logits: Optional[torch.Tensor] = None) -> None:
     """Router logits W_r h in 32-bit, sigmoid (or softmax) scores, the `top` largest per row: ids int32 [rows, top],
-    wts float32 [rows, top]."""
-    _cuda(h, w_router, ids, wts)
+    wts float32 [rows, top].  logits: float32 scratch [rows, experts] (made here when not given)."""
     n, width = h.shape
     E = w_router.shape[0]
+    if logits is None:
+        logits = torch.empty(n, E, dtype=torch.float32, device=h.device)
+    _cuda(h, w_router, ids, wts, logits)
+    _need(logits.dtype == torch.float32 and logits.numel() >= n * E, "moe_route: logits float32 [rows, experts]")
     _need(w_router.dtype == torch.float32 and w_router.shape[1] == width, "moe_route: router float32 [experts, width]")
     _need(ids.dtype == torch.int32 and wts.dtype == torch.float32 and ids.numel() >= n * top and wts.numel() >= n * top,
           "moe_route: ids int32 and wts float32 [rows, top]")
     _check(_lib.kernels().imparo_moe_route(_ptr(h), _code(h), _ptr(w_router), n, width, E, int(top), int(bool(softmax)),
-                                           int(bool(renormalise)), _ptr(ids), _ptr(wts), _stream()), "moe_route")
+                                           int(bool(renormalise)), _ptr(logits), _ptr(ids), _ptr(wts), _stream()), "moe_route")
+    COUNTS["own"] += 1
 
 
 MOE_GROUP_FROM = 32          # steps with at least this many (row, choice) pairs per expert on average run grouped by expert

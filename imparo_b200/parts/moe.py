@@ -68,7 +68,8 @@ class RoutedExperts(Part):
         ws = rt.workspace
         ids = ws.get("moe_ids", (T, self.top), torch.int32, first="tokens")
         wts = ws.get("moe_wts", (T, self.top), torch.float32, first="tokens")
-        ops.moe_route(x, self.w_router, self.top, ids, wts, softmax=self.score == "softmax", renormalise=self.renormalise)
+        ops.moe_route(x, self.w_router, self.top, ids, wts, softmax=self.score == "softmax", renormalise=self.renormalise,
+                      logits=ws.get("moe_logits", (T, self.experts), torch.float32, first="tokens"))
         pairs = T * self.top
         if pairs >= self.TILES_FROM and ops.moe_tiles_usable(x, self.w_gu):
             # many rows in bfloat16: sorted into tiles of 128 rows per expert, both products on the tensor-memory kernel
