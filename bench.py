@@ -335,10 +335,10 @@ def workload_vipotar(args):
 
 def negotar_config(width, layers, heads, kv_heads, head, ssm_heads, ssm_vdim, ssm_state, experts, top, ff, vocab):
     """A Negotar config.json of the given sizes: attention and state-space layers in turn (the first an attention layer),
-    every head rotated with rescaled frequencies, scores capped at 30, values shared from the first attention layer,
+    every head rotated with rescaled frequencies, scores capped at 50, values shared from the first attention layer,
     `experts` experts of `ff` features of which a token uses `top`."""
-    attn = {"heads": heads, "kv_heads": kv_heads, "dim": head, "vdim": head, "scale": head ** -0.5 * 8.0, "softcap": 30.0,
-            "v_mix": True, "rot": {"dims": head, "base": 500000.0, "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 2048}}}
+    attn = {"heads": heads, "kv_heads": kv_heads, "dim": head, "vdim": head, "scale": head ** -0.5 * 8.0, "softcap": 50.0,
+            "v_mix": True, "rot": {"dims": head, "base": 500000.0, "scaling": {"factor": 4.0, "low": 1.0, "high": 8.0, "original": 4096}}}
     ssm = {"heads": ssm_heads, "vdim": ssm_vdim, "state": ssm_state, "groups": 1, "conv": 4, "norm_groups": 1}
     mlp = {"kind": "moe", "router": {"experts": experts, "top": top}, "expert": {"ff": ff}}
     return {"architecture": "Negotar", "vocab": vocab, "width": width, "norm": {"eps": 1e-5}, "logit_scale": 1.0,

@@ -299,8 +299,8 @@ def _plain_attention_from_rows(m, eps, rows, bias, v_first=None, lam=None):
 @pytest.mark.parametrize("nh,nkv,hd,vd,rot,cap,blend", [
     (4, 2, 16, 24, {"dims": 8, "base": 300.0, "scaling": {"factor": 4.0, "low": 1.0, "high": 4.0, "original": 32}}, 5.0, True),
     (6, 1, 24, 8, None, None, False),
-    (3, 3, 32, 32, {"dims": 32, "base": 500.0}, 30.0, True),
-    (8, 1, 96, 64, {"dims": 48, "base": 1e6, "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 64}}, 2.0, False),
+    (3, 3, 32, 32, {"dims": 32, "base": 500.0}, 25.0, True),
+    (8, 1, 80, 48, {"dims": 48, "base": 250000.0, "scaling": {"factor": 6.0, "low": 1.0, "high": 3.0, "original": 64}}, 2.0, False),
     (2, 1, 40, 200, {"dims": 6, "base": 20.0}, None, True)])
 def test_prepared_heads_and_capped_attention_kernels(dtype, nh, nkv, hd, vd, rot, cap, blend):
     """Biases, rotation with rescaled frequencies, the norm without a weight, blended values and the soft cap: a prompt of
