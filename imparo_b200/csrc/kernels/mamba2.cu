@@ -117,7 +117,8 @@ __device__ __forceinline__ void state_step_no_out(float (&S)[NMAX], const float*
 }
 
 // A row's B and C entries of this lane within its warp's share of the state (n = n0 + lane, n0 + lane + 32, ...), its step
-// size and its x value, fetched one row ahead of the row being computed, so that their latency hides behind the arithmetic.
+// size and its x value, fetched ahead of the row being computed (the kernels keep two rows in flight), so that their latency
+// hides behind the arithmetic.
 template <int NH>
 struct RowAhead {
     static constexpr int PER = (NH + 31) / 32;
@@ -176,15 +177,17 @@ mamba2_scan_kernel(const float* __restrict__ xbc, const float* __restrict__ dt, 
     float S[NH];
 #pragma unroll
     for (int n = 0; n < NH; ++n) S[n] = (live && n0 + n < N) ? sp[(size_t)(n0 + n) * vdim] : 0.f;
-    RowAhead<NH> next;
+    RowAhead<NH> next, after;                          // the rows one and two ahead of the one being computed
     const int b_off = inner + g * N, c_off = inner + groups * N + g * N, x_col = h * vdim + p;
     if (first < last) next.fetch(xbc, dt, first, channels, b_off, c_off, x_col, heads, h, n0, N, lane, live, true);
+    if (first + 1 < last) after.fetch(xbc, dt, first + 1, channels, b_off, c_off, x_col, heads, h, n0, N, lane, live, true);
     for (int t = first; t < last; ++t) {
         __syncwarp();
         next.put(bc[warp][0], bc[warp][1], lane);
         __syncwarp();
         const float step = next.step, xv = next.x;
-        if (t + 1 < last) next.fetch(xbc, dt, t + 1, channels, b_off, c_off, x_col, heads, h, n0, N, lane, live, true);
+        next = after;
+        if (t + 2 < last) after.fetch(xbc, dt, t + 2, channels, b_off, c_off, x_col, heads, h, n0, N, lane, live, true);
         float acc = state_step<NH>(S, bc[warp][0], bc[warp][1], expf(a * step), step * xv);
         if (SPLIT > 1) {
             const int buf = (t - first) & 1;
@@ -247,15 +250,17 @@ mamba2_chunk_state_kernel(const float* __restrict__ xbc, const float* __restrict
 #pragma unroll
     for (int n = 0; n < NH; ++n) S[n] = 0.f;
     float total = 0.f;                                            // sum of a * dt over the chunk
-    RowAhead<NH> next;
+    RowAhead<NH> next, after;
     const int b_off = inner + g * N, x_col = h * vdim + p;
     next.fetch(xbc, dt, lo, channels, b_off, 0, x_col, heads, h, n0, N, lane, live, false);
+    if (lo + 1 < hi) after.fetch(xbc, dt, lo + 1, channels, b_off, 0, x_col, heads, h, n0, N, lane, live, false);
     for (int t = lo; t < hi; ++t) {
         __syncwarp();
         next.put(bs[warp], nullptr, lane);
         __syncwarp();
         const float step = next.step, xv = next.x;
-        if (t + 1 < hi) next.fetch(xbc, dt, t + 1, channels, b_off, 0, x_col, heads, h, n0, N, lane, live, false);
+        next = after;
+        if (t + 2 < hi) after.fetch(xbc, dt, t + 2, channels, b_off, 0, x_col, heads, h, n0, N, lane, live, false);
         total += a * step;
         state_step_no_out<NH>(S, bs[warp], expf(a * step), step * xv);
     }
@@ -335,15 +340,17 @@ mamba2_chunk_out_kernel(const float* __restrict__ xbc, const float* __restrict__
     float S[NH];
 #pragma unroll
     for (int n = 0; n < NH; ++n) S[n] = (live && n0 + n < N) ? sp[(size_t)(n0 + n) * vdim] : 0.f;
-    RowAhead<NH> next;
+    RowAhead<NH> next, after;
     const int b_off = inner + g * N, c_off = inner + groups * N + g * N, x_col = h * vdim + p;
     next.fetch(xbc, dt, lo, channels, b_off, c_off, x_col, heads, h, n0, N, lane, live, true);
+    if (lo + 1 < hi) after.fetch(xbc, dt, lo + 1, channels, b_off, c_off, x_col, heads, h, n0, N, lane, live, true);
     for (int t = lo; t < hi; ++t) {
         __syncwarp();
         next.put(bc[warp][0], bc[warp][1], lane);
         __syncwarp();
         const float step = next.step, xv = next.x;
-        if (t + 1 < hi) next.fetch(xbc, dt, t + 1, channels, b_off, c_off, x_col, heads, h, n0, N, lane, live, true);
+        next = after;
+        if (t + 2 < hi) after.fetch(xbc, dt, t + 2, channels, b_off, c_off, x_col, heads, h, n0, N, lane, live, true);
         float acc = state_step<NH>(S, bc[warp][0], bc[warp][1], expf(a * step), step * xv);
         if (SPLIT > 1) {
             const int buf = (t - lo) & 1;
