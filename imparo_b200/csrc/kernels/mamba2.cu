@@ -9,7 +9,8 @@
 //      S[:, p] in their registers (a stretch each):  S = exp(-exp(A_log) dt) S + dt B x[p];  y[p] = C . S + D x[p].  Decays, step sizes
 //      and the state are 32-bit in both precisions.
 //  (3) Long portions run in chunks of L rows side by side (three launches, as the decayed linear attention does):
-//      every chunk's own state from zero and its total decay; a scan over each request's chunks that leaves every
+//      every chunk's own state from zero and its total decay (as a product of weighted B rows with x rows for states up
+//      to 128, else by walking the rows); a scan over each request's chunks that leaves every
 //      chunk's starting state and the request's new state; every chunk's outputs from its starting state plus the
 //      rows inside the chunk.  32-bit on CUDA cores.
 //  (4) gate_group_rmsnorm: y * silu(z), then an RMS norm over each of `groups` equal stretches of the row, times a
@@ -273,6 +274,65 @@ mamba2_chunk_state_kernel(const float* __restrict__ xbc, const float* __restrict
     if (threadIdx.x == 0 && blockIdx.z == 0) chunk_decay[(size_t)c * heads + h] = total;
 }
 
+// The same as a product, for state sizes up to 128 and chunks of up to 64 rows: with w_t = dt_t exp(sum over the rows r
+// after t of a dt_r), the chunk's own state is S[n, p] = sum_t (w_t B_t[n]) x_t[p].  A block per (head, chunk, 32 value
+// columns): the weighted B rows and the x rows in shared memory, every thread a patch of 4 x 4 of S, rows added in order.
+// grid (heads, chunks, ceil(vdim / 32)), 256 threads
+constexpr int SM_L = 64, SM_N = 128, SM_P = 32;
+__global__ void __launch_bounds__(256)
+mamba2_chunk_state_mm_kernel(const float* __restrict__ xbc, const float* __restrict__ dt, const float* __restrict__ A_log,
+                             const int* __restrict__ chunk_lo, const int* __restrict__ chunk_hi,
+                             float* __restrict__ chunk_state, float* __restrict__ chunk_decay,
+                             int heads, int vdim, int N, int groups) {
+    __shared__ __align__(16) float bw[SM_L][SM_N];
+    __shared__ __align__(16) float xs[SM_L][SM_P];
+    __shared__ float adt[SM_L], wt[SM_L];
+    pdl_trigger();
+    const int h = blockIdx.x, c = blockIdx.y, p0 = blockIdx.z * SM_P, tid = threadIdx.x;
+    const float a = -expf(A_log[h]);
+    pdl_wait();
+    const int lo = chunk_lo[c], hi = chunk_hi[c];
+    if (lo >= hi) return;
+    const int len = hi - lo;
+    const int inner = heads * vdim, channels = inner + 2 * groups * N;
+    const int g = h / (heads / groups);
+    if (tid < SM_L) adt[tid] = tid < len ? a * dt[(size_t)(lo + tid) * heads + h] : 0.f;
+    __syncthreads();
+    if (tid < SM_L) {
+        float after = 0.f;                                        // sum of a dt over the rows after this one, last row first
+        for (int r = len - 1; r > tid; --r) after += adt[r];
+        wt[tid] = tid < len ? dt[(size_t)(lo + tid) * heads + h] * expf(after) : 0.f;
+        if (tid == 0 && blockIdx.z == 0) chunk_decay[(size_t)c * heads + h] = after + adt[0];
+    }
+    __syncthreads();
+    for (int i = tid; i < SM_L * SM_N; i += 256) {
+        const int t = i / SM_N, n = i - t * SM_N;
+        bw[t][n] = (t < len && n < N) ? wt[t] * xbc[(size_t)(lo + t) * channels + inner + g * N + n] : 0.f;
+    }
+    for (int i = tid; i < SM_L * SM_P; i += 256) {
+        const int t = i / SM_P, pp = i - t * SM_P;
+        xs[t][pp] = (t < len && p0 + pp < vdim) ? xbc[(size_t)(lo + t) * channels + h * vdim + p0 + pp] : 0.f;
+    }
+    __syncthreads();
+    const int tn = (tid >> 3) * 4, tp = (tid & 7) * 4;             // 32 x 8 threads, a patch of 4 state entries x 4 columns each
+    float acc[4][4] = {};
+    for (int t = 0; t < len; ++t) {
+        const float4 b4 = *reinterpret_cast<const float4*>(&bw[t][tn]);
+        const float4 x4 = *reinterpret_cast<const float4*>(&xs[t][tp]);
+        const float bv[4] = {b4.x, b4.y, b4.z, b4.w}, xv[4] = {x4.x, x4.y, x4.z, x4.w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+#pragma unroll
+            for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(bv[i], xv[j], acc[i][j]);
+    }
+    float* out = chunk_state + (((size_t)c * heads + h) * N) * vdim;
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+            if (tn + i < N && p0 + tp + j < vdim) out[(size_t)(tn + i) * vdim + p0 + tp + j] = acc[i][j];
+}
+
 // per request and head: chunk_state[c] becomes the state BEFORE chunk c; the slot gets the state after the last chunk
 __global__ void __launch_bounds__(256)
 mamba2_chunk_scan_kernel(float* __restrict__ chunk_state, const float* __restrict__ chunk_decay,
@@ -292,15 +352,15 @@ mamba2_chunk_scan_kernel(float* __restrict__ chunk_state, const float* __restric
         float* sp = state + ((size_t)slot * heads + h) * per + e;
         float S = *sp;
         int c = c0;
-        for (; c + 4 <= c1; c += 4) {                              // four chunks' loads in flight
-            float own[4], dec[4];
+        for (; c + 8 <= c1; c += 8) {                              // eight chunks' loads in flight
+            float own[8], dec[8];
 #pragma unroll
-            for (int u = 0; u < 4; ++u) {
+            for (int u = 0; u < 8; ++u) {
                 own[u] = chunk_state[((size_t)(c + u) * heads + h) * per + e];
                 dec[u] = expf(chunk_decay[(size_t)(c + u) * heads + h]);
             }
 #pragma unroll
-            for (int u = 0; u < 4; ++u) {
+            for (int u = 0; u < 8; ++u) {
                 chunk_state[((size_t)(c + u) * heads + h) * per + e] = S;
                 S = dec[u] * S + own[u];
             }
@@ -466,10 +526,15 @@ extern "C" int imparo_mamba2_scan_chunked(const float* xbc, const float* dt, con
            chunk_hi, item_chunk_start);
     IMPARO_CHECK_LAUNCH();
     dim3 grid(heads, max_chunks, (vdim + 31) / 32);
+    if (N <= SM_N && L <= SM_L) {
+        launch(mamba2_chunk_state_mm_kernel, grid, dim3(256), 0, stream, xbc, dt, A_log, (const int*)chunk_lo, (const int*)chunk_hi,
+               chunk_state, chunk_decay, heads, vdim, N, groups);
+    } else {
 #define CALL(NH, SP) launch(mamba2_chunk_state_kernel<NH, SP>, grid, dim3(32 * SP), 0, stream, xbc, dt, A_log, (const int*)chunk_lo, \
                             (const int*)chunk_hi, chunk_state, chunk_decay, heads, vdim, N, groups)
-    MAMBA2_BY_N(CALL);
+        MAMBA2_BY_N(CALL);
 #undef CALL
+    }
     IMPARO_CHECK_LAUNCH();
     const int per = N * vdim;
     launch(mamba2_chunk_scan_kernel, dim3(heads, n_items, (per + 255) / 256), dim3(256), 0, stream, chunk_state,
