@@ -129,8 +129,10 @@ moe_logits_kernel(const T* __restrict__ h, const float* __restrict__ w_r, int n_
 }
 
 // The choice: a warp per row, four rows per block
+// logits: [n_rows, parts * experts]; a logit is the sum of its `parts` entries, experts apart, added in order (parts > 1:
+// the router matrix was cut into bfloat16 pieces whose sum is the 32-bit matrix to its last bit, see imparo_moe_pick)
 __global__ void __launch_bounds__(128)
-moe_pick_kernel(const float* __restrict__ logits, int n_rows, int experts, int top, int softmax_scores, int renormalise,
+moe_pick_kernel(const float* __restrict__ logits, int n_rows, int experts, int parts, int top, int softmax_scores, int renormalise,
                 int* __restrict__ ids, float* __restrict__ wts) {
     extern __shared__ __align__(16) float pick_smem[];   // [4][experts]
     pdl_trigger();
@@ -139,7 +141,12 @@ moe_pick_kernel(const float* __restrict__ logits, int n_rows, int experts, int t
     const int r = blockIdx.x * 4 + warp;
     if (r >= n_rows) return;
     float* s = pick_smem + (size_t)warp * experts;
-    for (int e = lane; e < experts; e += 32) s[e] = logits[(size_t)r * experts + e];
+    for (int e = lane; e < experts; e += 32) {
+        const float* l = logits + (size_t)r * parts * experts + e;
+        float v = l[0];
+        for (int k = 1; k < parts; ++k) v += l[(size_t)k * experts];
+        s[e] = v;
+    }
     __syncwarp();
     // The choice goes by the logits: scores are monotone in them, and a sigmoid that has reached 1 in 32-bit would tie.
     float m = -INFINITY, l = 1.f;
@@ -602,7 +609,21 @@ extern "C" int imparo_moe_route(const void* h, int dtype, const float* w_r, int 
     else return -1;
     IMPARO_CHECK_LAUNCH();
     launch(moe_pick_kernel, dim3((n_rows + 3) / 4), dim3(128), (size_t)4 * experts * sizeof(float), stream, (const float*)logits, n_rows,
-           experts, top, softmax_scores, renormalise, ids, wts);
+           experts, 1, top, softmax_scores, renormalise, ids, wts);
+    IMPARO_CHECK_LAUNCH();
+    return 0;
+}
+
+// The choice alone, from logits that a product has made: [n_rows, parts * experts] float32.  With bfloat16 rows h (exact in
+// 32-bit) and the 32-bit router matrix cut into three bfloat16 pieces (w1 = W rounded, w2 = W - w1 rounded, w3 the rest
+// rounded: 8 + 8 + 8 bits of mantissa, their sum is W to its last bit), the
+// tensor-core product h [w1; w2; w3]^T has exact products and 32-bit sums: the router's logits in 32-bit, at the product's speed.
+extern "C" int imparo_moe_pick(const float* logits, int n_rows, int experts, int parts, int top, int softmax_scores, int renormalise,
+                               int* ids, float* wts, cudaStream_t stream) {
+    if (n_rows <= 0) return 0;
+    if (top < 1 || top > experts || top > 32 || experts > 2048 || parts < 1 || parts > 4) return -2;
+    launch(moe_pick_kernel, dim3((n_rows + 3) / 4), dim3(128), (size_t)4 * experts * sizeof(float), stream, logits, n_rows, experts,
+           parts, top, softmax_scores, renormalise, ids, wts);
     IMPARO_CHECK_LAUNCH();
     return 0;
 }

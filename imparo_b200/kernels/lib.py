@@ -127,6 +127,7 @@ def _declare_kernels(lib):
     _declare(lib, "imparo_gate_group_rmsnorm", [P, P, I, c_int64, P, c_float, P, I, I, I, I, S])
     _declare(lib, "imparo_moe_route", [P, I, P, I, I, I, I, I, I, P, P, P, S])
     _declare(lib, "imparo_moe_rows", [P, P, P, I, P, P, I, I, I, I, I, I, P, P, S])
+    _declare(lib, "imparo_moe_pick", [P, I, I, I, I, I, I, P, P, S])
     _declare(lib, "imparo_moe_tiles", [P, P, P, P, P, I, I, I, I, I, I, P, P, P, P, P, P, S])
     _declare(lib, "imparo_moe_grouped", [P, P, P, I, P, P, I, I, I, I, I, I, P, P, P, P, S])
     _declare(lib, "imparo_linear_attention_recurrent", [P, P, P, c_int64, I, I, P, P, P, P, I, I, P, I, I, I, P, S])

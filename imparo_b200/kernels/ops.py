@@ -1302,6 +1302,19 @@ def moe_route(h: torch.Tensor, w_router: torch.Tensor, top: int, ids: torch.Tens
     COUNTS["own"] += 1
 
 
+def moe_pick(logits: torch.Tensor, experts: int, parts: int, top: int, ids: torch.Tensor, wts: torch.Tensor, softmax: bool = False,
+             renormalise: bool = False) -> None:
+    """The router's choice from logits a product has made: logits float32 [rows, parts * experts], a logit being the sum of
+    its `parts` entries `experts` apart (a 32-bit router matrix cut into bfloat16 pieces that add up to it to its last bit)."""
+    _cuda(logits, ids, wts)
+    n = logits.shape[0]
+    _need(logits.dtype == torch.float32 and logits.shape[1] == parts * experts, "moe_pick: logits float32 [rows, parts * experts]")
+    _need(ids.dtype == torch.int32 and wts.dtype == torch.float32 and ids.numel() >= n * top and wts.numel() >= n * top,
+          "moe_pick: ids int32 and wts float32 [rows, top]")
+    _check(_lib.kernels().imparo_moe_pick(_ptr(logits), n, int(experts), int(parts), int(top), int(bool(softmax)),
+                                          int(bool(renormalise)), _ptr(ids), _ptr(wts), _stream()), "moe_pick")
+
+
 MOE_GROUP_FROM = 32          # steps with at least this many (row, choice) pairs per expert on average run grouped by expert
 
 

@@ -56,6 +56,16 @@ class RoutedExperts(Part):
     def bind(self, tensors):
         n = self.names
         self.w_router = tensors[n["router"]]
+        # For bfloat16 rows the router's logits come from the tensor-core product: the 32-bit matrix cut into three
+        # bfloat16 pieces that add up to it to its last bit, so every product is exact and the sums are 32-bit.
+        self.w_router_pieces = None
+        if self.rt.act_dtype == torch.bfloat16:
+            rest, pieces = self.w_router.float(), []
+            for _ in range(3):
+                piece = rest.to(torch.bfloat16)
+                pieces.append(piece)
+                rest = rest - piece.float()
+            self.w_router_pieces = torch.cat(pieces, dim=0).contiguous()
         # experts stacked: [experts, 2 ff, hidden] = [gate; up] and [experts, hidden, ff]
         self.w_gu = torch.stack([torch.cat([tensors[n["gate"].format(e=e)], tensors[n["up"].format(e=e)]], dim=0)
                                  for e in range(self.experts)]).contiguous()
@@ -68,8 +78,13 @@ class RoutedExperts(Part):
         ws = rt.workspace
         ids = ws.get("moe_ids", (T, self.top), torch.int32, first="tokens")
         wts = ws.get("moe_wts", (T, self.top), torch.float32, first="tokens")
-        ops.moe_route(x, self.w_router, self.top, ids, wts, softmax=self.score == "softmax", renormalise=self.renormalise,
-                      logits=ws.get("moe_logits", (T, self.experts), torch.float32, first="tokens"))
+        if self.w_router_pieces is not None and x.dtype == torch.bfloat16:
+            logits = ws.get("moe_logits", (T, 3 * self.experts), torch.float32, first="tokens")
+            ops.linear(x, self.w_router_pieces, logits, status=rt.status)
+            ops.moe_pick(logits, self.experts, 3, self.top, ids, wts, softmax=self.score == "softmax", renormalise=self.renormalise)
+        else:
+            ops.moe_route(x, self.w_router, self.top, ids, wts, softmax=self.score == "softmax", renormalise=self.renormalise,
+                          logits=ws.get("moe_logits", (T, self.experts), torch.float32, first="tokens"))
         pairs = T * self.top
         if pairs >= self.TILES_FROM and ops.moe_tiles_usable(x, self.w_gu):
             # many rows in bfloat16: sorted into tiles of 128 rows per expert, both products on the tensor-memory kernel
