@@ -290,7 +290,7 @@ __global__ void softcap_kernel(float* __restrict__ x, size_t n, float cap) {
 template <typename TOut>
 __global__ void __launch_bounds__(256)
 out_norm_add_kernel(float* __restrict__ x, const float* __restrict__ y, const float* __restrict__ w, float eps, int width,
-                    TOut* __restrict__ copy) {
+                    TOut* __restrict__ copy, int vec) {
     __shared__ float scratch[33];
     pdl_trigger();
     pdl_wait();
@@ -298,6 +298,26 @@ out_norm_add_kernel(float* __restrict__ x, const float* __restrict__ y, const fl
     const float* yr = y + (size_t)r * width;
     float* xr = x + (size_t)r * width;
     float ss = 0.f;
+    if (vec) {                                     // width a multiple of 4 and every row 16-byte aligned
+        for (int i = threadIdx.x * 4; i < width; i += blockDim.x * 4) {
+            const float4 v = *reinterpret_cast<const float4*>(yr + i);
+            ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+        }
+        ss = block_sum(ss, scratch);
+        const float scale = 1.0f / sqrtf(ss / (float)width + eps);
+        for (int i = threadIdx.x * 4; i < width; i += blockDim.x * 4) {
+            const float4 v = *reinterpret_cast<const float4*>(yr + i);
+            const float4 ww = *reinterpret_cast<const float4*>(w + i);
+            float4 o = *reinterpret_cast<const float4*>(xr + i);
+            o.x += v.x * scale * ww.x; o.y += v.y * scale * ww.y; o.z += v.z * scale * ww.z; o.w += v.w * scale * ww.w;
+            *reinterpret_cast<float4*>(xr + i) = o;
+            if (copy) {
+                TOut* c = copy + (size_t)r * width + i;
+                c[0] = from_f32<TOut>(o.x); c[1] = from_f32<TOut>(o.y); c[2] = from_f32<TOut>(o.z); c[3] = from_f32<TOut>(o.w);
+            }
+        }
+        return;
+    }
     for (int i = threadIdx.x; i < width; i += blockDim.x) { const float v = yr[i]; ss += v * v; }
     ss = block_sum(ss, scratch);
     const float scale = 1.0f / sqrtf(ss / (float)width + eps);
@@ -456,10 +476,11 @@ extern "C" int imparo_softcap(float* x, long long n, float cap, cudaStream_t str
 extern "C" int imparo_out_norm_add(float* x, const float* y, const float* w, float eps, void* copy, int copy_dtype, int rows,
                                    int width, cudaStream_t stream) {
     if (rows <= 0) return 0;
+    const int vec = width % 4 == 0 && (((uintptr_t)x | (uintptr_t)y | (uintptr_t)w | (uintptr_t)copy) & 15) == 0;
     if (copy != nullptr && copy_dtype == IMPARO_DT_BF16)
-        launch(out_norm_add_kernel<__nv_bfloat16>, dim3(rows), dim3(256), 0, stream, x, y, w, eps, width, (__nv_bfloat16*)copy);
+        launch(out_norm_add_kernel<__nv_bfloat16>, dim3(rows), dim3(256), 0, stream, x, y, w, eps, width, (__nv_bfloat16*)copy, vec);
     else if (copy == nullptr || copy_dtype == IMPARO_DT_F32)
-        launch(out_norm_add_kernel<float>, dim3(rows), dim3(256), 0, stream, x, y, w, eps, width, (float*)copy);
+        launch(out_norm_add_kernel<float>, dim3(rows), dim3(256), 0, stream, x, y, w, eps, width, (float*)copy, vec);
     else return -1;
     IMPARO_CHECK_LAUNCH();
     return 0;
