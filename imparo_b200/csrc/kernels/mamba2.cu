@@ -58,51 +58,6 @@ mamba2_conv_kernel(const T* __restrict__ proj, size_t stride, int x_off, int dt_
     xbc[(size_t)t * channels + c] = silu(acc);
 }
 
-// The same for 32-bit rows whose channel stretches are multiples of four: a thread takes four channels of a row, 16 bytes
-// per load and store.  grid (rows, ceil(channels / 4 / 256))
-__global__ void __launch_bounds__(256)
-mamba2_conv4_kernel(const float* __restrict__ proj, size_t stride, int x_off, int channels, int taps,
-                    const float* __restrict__ w, const float* __restrict__ bias, const float* __restrict__ state,
-                    const int* __restrict__ item_row_start, const int* __restrict__ item_of_token,
-                    const int* __restrict__ item_slot, int n_slots, float* __restrict__ xbc, int* status) {
-    pdl_trigger();
-    const int t = blockIdx.x;
-    const int c = (blockIdx.y * blockDim.x + threadIdx.x) * 4;
-    const int item = item_of_token[t];
-    const int first = item_row_start[item];
-    const int slot = item_slot[item];
-    pdl_wait();
-    if (c >= channels) return;
-    if (slot < 0 || slot >= n_slots) {
-        if (c == 0) report(status, IMPARO_ST_SLOT_RANGE, 61, t, slot);
-        return;
-    }
-    const float* st = state + (size_t)slot * (taps - 1) * channels;
-    float4 acc = bias ? *reinterpret_cast<const float4*>(bias + c) : make_float4(0.f, 0.f, 0.f, 0.f);
-    const int j = t - first;
-    for (int k = 0; k < taps; ++k) {
-        const int src = j - (taps - 1 - k);
-        const float4 u = src >= 0 ? *reinterpret_cast<const float4*>(proj + (size_t)(first + src) * stride + x_off + c)
-                                  : *reinterpret_cast<const float4*>(st + (size_t)(taps - 1 + src) * channels + c);
-        acc.x += w[(size_t)c * taps + k] * u.x;
-        acc.y += w[(size_t)(c + 1) * taps + k] * u.y;
-        acc.z += w[(size_t)(c + 2) * taps + k] * u.z;
-        acc.w += w[(size_t)(c + 3) * taps + k] * u.w;
-    }
-    *reinterpret_cast<float4*>(xbc + (size_t)t * channels + c) = make_float4(silu(acc.x), silu(acc.y), silu(acc.z), silu(acc.w));
-}
-
-// the step sizes of a launch whose channels the kernel above takes: grid (rows), `heads` threads' worth of work
-__global__ void __launch_bounds__(128)
-mamba2_dt_kernel(const float* __restrict__ proj, size_t stride, int dt_off, int heads, const float* __restrict__ dt_bias,
-                 float* __restrict__ dt) {
-    pdl_trigger();
-    pdl_wait();
-    const int t = blockIdx.x;
-    for (int h = threadIdx.x; h < heads; h += blockDim.x)
-        dt[(size_t)t * heads + h] = softplus_f(proj[(size_t)t * stride + dt_off + h] + dt_bias[h]);
-}
-
 template <typename T>
 __global__ void __launch_bounds__(256)
 mamba2_conv_state_kernel(const T* __restrict__ proj, size_t stride, int x_off, int channels, int taps,
@@ -509,17 +464,8 @@ extern "C" int imparo_mamba2_conv(const void* proj, int dtype, long long stride,
     if (taps < 1 || taps > 17) return -6;
     dim3 grid(n_tok, (channels + heads + 255) / 256), sgrid(n_items, (channels + 255) / 256);
     if (dtype == IMPARO_DT_F32) {
-        const bool by4 = channels % 4 == 0 && x_off % 4 == 0 && stride % 4 == 0 && n_tok >= 64 &&
-                         (((uintptr_t)proj | (uintptr_t)xbc | (uintptr_t)state | (uintptr_t)bias) & 15) == 0;
-        if (by4) {
-            launch(mamba2_conv4_kernel, dim3(n_tok, (channels / 4 + 255) / 256), dim3(256), 0, stream, (const float*)proj, (size_t)stride,
-                   x_off, channels, taps, w, bias, (const float*)state, item_row_start, item_of_token, item_slot, n_slots, xbc, status);
-            IMPARO_CHECK_LAUNCH();
-            launch(mamba2_dt_kernel, dim3(n_tok), dim3(128), 0, stream, (const float*)proj, (size_t)stride, dt_off, heads, dt_bias, dt);
-        } else {
-            launch(mamba2_conv_kernel<float>, grid, dim3(256), 0, stream, (const float*)proj, (size_t)stride, x_off, dt_off, channels,
-                   heads, taps, w, bias, dt_bias, (const float*)state, item_row_start, item_of_token, item_slot, n_slots, xbc, dt, status);
-        }
+        launch(mamba2_conv_kernel<float>, grid, dim3(256), 0, stream, (const float*)proj, (size_t)stride, x_off, dt_off, channels, heads,
+               taps, w, bias, dt_bias, (const float*)state, item_row_start, item_of_token, item_slot, n_slots, xbc, dt, status);
         IMPARO_CHECK_LAUNCH();
         if (taps > 1)
             launch(mamba2_conv_state_kernel<float>, sgrid, dim3(256), 0, stream, (const float*)proj, (size_t)stride, x_off, channels, taps,

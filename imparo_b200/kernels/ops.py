@@ -1233,8 +1233,6 @@ def mamba2_conv(proj: torch.Tensor, x_off: int, dt_off: int, channels: int, head
                                              _ptr(status), _stream()), "mamba2_conv")
     if taps > 1:
         COUNTS["own"] += 1
-    if proj.dtype == torch.float32 and channels % 4 == 0 and x_off % 4 == 0 and proj.stride(0) % 4 == 0 and T >= 64:
-        COUNTS["own"] += 1          # four channels per thread, the step sizes in a launch of their own
 
 
 def mamba2_scan(xbc: torch.Tensor, dt: torch.Tensor, A_log: torch.Tensor, D: torch.Tensor, state: torch.Tensor, item_row_start,
